@@ -1,0 +1,237 @@
+// Shared device/host helpers for the sm_100a row-normalization kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fln_b200.h"
+
+namespace fln {
+
+// ------------------------------------------------------------------------------------
+// element conversion
+// ------------------------------------------------------------------------------------
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+// ------------------------------------------------------------------------------------
+// VEC elements moved by one load/store instruction (2, 4, 8 or 16 bytes)
+// ------------------------------------------------------------------------------------
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) Pack {
+  T e[VEC];
+};
+
+template <int BYTES>
+struct Raw;
+template <>
+struct Raw<16> {
+  using type = uint4;
+};
+template <>
+struct Raw<8> {
+  using type = uint2;
+};
+template <>
+struct Raw<4> {
+  using type = unsigned int;
+};
+template <>
+struct Raw<2> {
+  using type = unsigned short;
+};
+template <>
+struct Raw<1> {
+  using type = unsigned char;
+};
+
+// streaming load: the matrices are touched once per kernel, keep them out of the way of
+// gamma/beta in L1/L2
+template <typename T, int VEC>
+__device__ __forceinline__ Pack<T, VEC> ld_stream(const T* p) {
+  using R = typename Raw<sizeof(T) * VEC>::type;
+  Pack<T, VEC> out;
+  *reinterpret_cast<R*>(&out) = __ldcs(reinterpret_cast<const R*>(p));
+  return out;
+}
+// cached read-only load (parameters, re-read by every CTA)
+template <typename T, int VEC>
+__device__ __forceinline__ Pack<T, VEC> ld_param(const T* p) {
+  using R = typename Raw<sizeof(T) * VEC>::type;
+  Pack<T, VEC> out;
+  *reinterpret_cast<R*>(&out) = __ldg(reinterpret_cast<const R*>(p));
+  return out;
+}
+// plain load (data that a later kernel of ours wants to find in L2)
+template <typename T, int VEC>
+__device__ __forceinline__ Pack<T, VEC> ld_plain(const T* p) {
+  using R = typename Raw<sizeof(T) * VEC>::type;
+  Pack<T, VEC> out;
+  *reinterpret_cast<R*>(&out) = *reinterpret_cast<const R*>(p);
+  return out;
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void st_stream(T* p, const Pack<T, VEC>& v) {
+  using R = typename Raw<sizeof(T) * VEC>::type;
+  __stcs(reinterpret_cast<R*>(p), *reinterpret_cast<const R*>(&v));
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void st_plain(T* p, const Pack<T, VEC>& v) {
+  using R = typename Raw<sizeof(T) * VEC>::type;
+  *reinterpret_cast<R*>(p) = *reinterpret_cast<const R*>(&v);
+}
+
+// ------------------------------------------------------------------------------------
+// activations
+// ------------------------------------------------------------------------------------
+template <int ACT>
+__device__ __forceinline__ float apply_act(float v) {
+  if (ACT == FLN_ACT_GELU_TANH) {
+    // 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))
+    const float s = 0.7978845608028654f;
+    const float a = 0.044715f;
+    float v3 = v * v * v;
+    return 0.5f * v * (1.0f + tanhf(s * (v + a * v3)));
+  } else if (ACT == FLN_ACT_GELU_ERF) {
+    return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+  }
+  return v;
+}
+
+// ------------------------------------------------------------------------------------
+// row-group reductions.  A row is owned by `tpr` consecutive threads (power of two).
+// tpr <= 32: the group is a slice of one warp.  tpr > 32: the group is tpr/32 whole warps
+// and partial results take one hop through shared memory.
+// ------------------------------------------------------------------------------------
+struct Wf {  // running (mean, M2, count)
+  float mean, m2, n;
+};
+
+__device__ __forceinline__ Wf wf_merge(Wf a, Wf b) {
+  // Chan et al. pairwise update.  Written so that equal means give delta == 0 exactly
+  // (constant rows keep M2 == 0) and empty partners (n == 0) are harmless.
+  float n = a.n + b.n;
+  float rn = n > 0.f ? __frcp_rn(n) : 0.f;
+  float delta = b.mean - a.mean;
+  Wf o;
+  o.n = n;
+  o.mean = a.mean + delta * (b.n * rn);
+  o.m2 = a.m2 + b.m2 + delta * delta * (a.n * b.n * rn);
+  return o;
+}
+
+__device__ __forceinline__ Wf wf_shfl_xor(Wf v, int off) {
+  Wf o;
+  o.mean = __shfl_xor_sync(0xffffffffu, v.mean, off);
+  o.m2 = __shfl_xor_sync(0xffffffffu, v.m2, off);
+  o.n = __shfl_xor_sync(0xffffffffu, v.n, off);
+  return o;
+}
+
+// smem: 3 * 32 floats per buffer.  Every thread of the CTA must call this.
+__device__ __forceinline__ Wf group_reduce_wf(Wf v, int tpr, float* smem) {
+  const int lane = threadIdx.x & 31;
+  const int lim = tpr < 32 ? tpr : 32;
+  for (int off = lim >> 1; off > 0; off >>= 1) v = wf_merge(v, wf_shfl_xor(v, off));
+  if (tpr > 32) {
+    const int warp = threadIdx.x >> 5;
+    const int wpr = tpr >> 5;  // warps per row
+    const int gbase = (warp / wpr) * wpr;
+    if (lane == 0) {
+      smem[warp] = v.mean;
+      smem[32 + warp] = v.m2;
+      smem[64 + warp] = v.n;
+    }
+    __syncthreads();
+    Wf w;
+    if (lane < wpr) {
+      w.mean = smem[gbase + lane];
+      w.m2 = smem[32 + gbase + lane];
+      w.n = smem[64 + gbase + lane];
+    } else {
+      w.mean = 0.f;
+      w.m2 = 0.f;
+      w.n = 0.f;
+    }
+    for (int off = wpr >> 1; off > 0; off >>= 1) w = wf_merge(w, wf_shfl_xor(w, off));
+    v = w;
+  }
+  // the two partners of a merge round differently; make the whole group agree
+  const int src = tpr < 32 ? (lane & ~(tpr - 1)) : 0;
+  v.mean = __shfl_sync(0xffffffffu, v.mean, src);
+  v.m2 = __shfl_sync(0xffffffffu, v.m2, src);
+  return v;
+}
+
+// sum of NV values per thread over the row group; all threads get bit-identical results.
+// smem: NV * 32 floats per buffer.
+template <int NV>
+__device__ __forceinline__ void group_reduce_sum(float (&v)[NV], int tpr, float* smem) {
+  const int lane = threadIdx.x & 31;
+  const int lim = tpr < 32 ? tpr : 32;
+  for (int off = lim >> 1; off > 0; off >>= 1) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+  }
+  if (tpr > 32) {
+    const int warp = threadIdx.x >> 5;
+    const int wpr = tpr >> 5;
+    const int gbase = (warp / wpr) * wpr;
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) smem[i * 32 + warp] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = lane < wpr ? smem[i * 32 + gbase + lane] : 0.f;
+    for (int off = wpr >> 1; off > 0; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host side: launch plan
+// ------------------------------------------------------------------------------------
+struct Plan {
+  int generic;  // 1: use the looping fallback kernel
+  int vec;      // elements per vector access
+  int K;        // vectors per thread (1, 2, 4, 8)
+  int tpr;      // threads per row (power of two)
+  int log2_tpr;
+  int threads;  // per CTA
+  int rows_per_cta;
+};
+
+int sm_count();  // of the current device, cached
+Plan make_plan(bool backward, int64_t rows, int cols, int elem_bytes, bool aligned16);
+void plan_override(int* K, int* tpr);
+
+inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define FLN_CHECK_LAUNCH()                                   \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return FLN_ERR_LAUNCH;           \
+  } while (0)
+
+}  // namespace fln

@@ -1,0 +1,341 @@
+// Row-wise LayerNorm / RMSNorm forward for sm_100a.
+//
+// One row is owned by `tpr` consecutive threads; each thread keeps K vectors of the row in
+// registers, so the row is read from HBM exactly once.  Statistics are fp32: per-thread
+// two-pass (mean, M2) over the registers, then a (mean, M2, count) merge across the group
+// by warp shuffles and at most one hop through shared memory.  The epilogue (affine,
+// GELU, down-cast) is applied on the registers and stored with 16-byte vector stores.
+//
+// Stands in for layernorm_kernel / layernorm_gelu_kernel of the reference
+// (csrc/layernorm_cuda_kernel.cu:39-92, 95-148), which read every row three times with
+// scalar loads, and for layernorm_forward_kernel_optimized
+// (csrc/layernorm_cuda_kernel_optimized.cu:54-168), whose mean/rstd outputs it keeps.
+#include "fln_common.cuh"
+
+namespace fln {
+
+struct FwdParams {
+  const void* x;
+  const void* res;
+  const void* gamma;
+  const void* beta;
+  void* y;
+  void* sum_out;
+  float* mean;
+  float* rstd;
+  int64_t rows;
+  int cols;
+  int nv;  // vectors per row
+  int tpr;
+  int log2_tpr;
+  float eps;
+};
+
+template <int K>
+struct MaxThreads {
+  static constexpr int value = K <= 2 ? 1024 : 512;
+};
+
+template <typename TI, typename TO, int VEC, int K, int KIND, int ACT>
+__global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const FwdParams p) {
+  __shared__ float s_red[96];
+
+  const int tid = threadIdx.x;
+  const int tpr = p.tpr;
+  const int lane_r = tid & (tpr - 1);
+  const int row_in_cta = tid >> p.log2_tpr;
+  const int rows_per_cta = blockDim.x >> p.log2_tpr;
+  const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
+  const bool row_ok = row < p.rows;
+  const int64_t base = row * (int64_t)p.cols;
+
+  const TI* __restrict__ xr = reinterpret_cast<const TI*>(p.x) + base;
+
+  Pack<TI, VEC> raw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (row_ok && iv < p.nv) {
+      raw[k] = ld_stream<TI, VEC>(xr + (int64_t)iv * VEC);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) raw[k].e[i] = Cvt<TI>::from_f(0.f);
+    }
+  }
+  if (p.res != nullptr) {
+    // s = x + residual, rounded to the I/O type first: that rounded value is what gets
+    // normalized and what the residual stream carries on.
+    const TI* __restrict__ rr = reinterpret_cast<const TI*>(p.res) + base;
+    TI* __restrict__ sr = reinterpret_cast<TI*>(p.sum_out) + base;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (row_ok && iv < p.nv) {
+        Pack<TI, VEC> r = ld_stream<TI, VEC>(rr + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          raw[k].e[i] = Cvt<TI>::from_f(Cvt<TI>::to_f(raw[k].e[i]) + Cvt<TI>::to_f(r.e[i]));
+        st_stream<TI, VEC>(sr + (int64_t)iv * VEC, raw[k]);
+      }
+    }
+  }
+
+  // ---- statistics -------------------------------------------------------------------
+  float mean = 0.f, rstd;
+  if (KIND == FLN_LAYERNORM) {
+    float lsum = 0.f, cnt = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (iv < p.nv) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) lsum += Cvt<TI>::to_f(raw[k].e[i]);
+        cnt += (float)VEC;
+      }
+    }
+    Wf w;
+    w.n = cnt;
+    w.mean = cnt > 0.f ? lsum / cnt : 0.f;
+    w.m2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (iv < p.nv) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float d = Cvt<TI>::to_f(raw[k].e[i]) - w.mean;
+          w.m2 += d * d;
+        }
+      }
+    }
+    w = group_reduce_wf(w, tpr, s_red);
+    mean = w.mean;
+    float var = w.m2 / (float)p.cols;
+    rstd = 1.0f / sqrtf(var + p.eps);
+  } else {
+    float ss[1] = {0.f};
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float v = Cvt<TI>::to_f(raw[k].e[i]);  // padding vectors are zero
+        ss[0] += v * v;
+      }
+    }
+    group_reduce_sum<1>(ss, tpr, s_red);
+    rstd = 1.0f / sqrtf(ss[0] / (float)p.cols + p.eps);
+  }
+  if (row_ok && lane_r == 0) {
+    if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
+    if (p.rstd != nullptr) p.rstd[row] = rstd;
+  }
+
+  // ---- normalize + epilogue ---------------------------------------------------------
+  const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
+  const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
+  TO* __restrict__ yr = reinterpret_cast<TO*>(p.y) + base;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (row_ok && iv < p.nv) {
+      float v[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
+      if (gp != nullptr) {
+        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
+      }
+      if (bp != nullptr) {
+        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
+      }
+      Pack<TO, VEC> o;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o.e[i] = Cvt<TO>::from_f(apply_act<ACT>(v[i]));
+      st_stream<TO, VEC>(yr + (int64_t)iv * VEC, o);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Fallback for rows that do not fit the register budget or are too ragged for it:
+// one CTA per row, the row is re-read (it sits in L1/L2 after the first pass).
+// ----------------------------------------------------------------------------------------
+template <typename TI, typename TO, int KIND, int ACT>
+__global__ void __launch_bounds__(512) norm_fwd_generic_kernel(const FwdParams p) {
+  __shared__ float s_red[2][96];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * (int64_t)p.cols;
+  const TI* __restrict__ xr = reinterpret_cast<const TI*>(p.x) + base;
+  const TI* __restrict__ rr = p.res ? reinterpret_cast<const TI*>(p.res) + base : nullptr;
+  TI* __restrict__ sr = p.res ? reinterpret_cast<TI*>(p.sum_out) + base : nullptr;
+  const int tpr = blockDim.x;
+
+  auto load_s = [&](int j) -> float {
+    float v = Cvt<TI>::to_f(xr[j]);
+    if (rr != nullptr) v = Cvt<TI>::to_f(Cvt<TI>::from_f(v + Cvt<TI>::to_f(rr[j])));
+    return v;
+  };
+
+  float mean = 0.f, rstd;
+  if (KIND == FLN_LAYERNORM) {
+    float s1[1] = {0.f};
+    for (int j = threadIdx.x; j < p.cols; j += blockDim.x) s1[0] += load_s(j);
+    group_reduce_sum<1>(s1, tpr, s_red[0]);
+    mean = s1[0] / (float)p.cols;
+    float s2[1] = {0.f};
+    for (int j = threadIdx.x; j < p.cols; j += blockDim.x) {
+      float d = load_s(j) - mean;
+      s2[0] += d * d;
+    }
+    group_reduce_sum<1>(s2, tpr, s_red[1]);
+    rstd = 1.0f / sqrtf(s2[0] / (float)p.cols + p.eps);
+  } else {
+    float s2[1] = {0.f};
+    for (int j = threadIdx.x; j < p.cols; j += blockDim.x) {
+      float v = load_s(j);
+      s2[0] += v * v;
+    }
+    group_reduce_sum<1>(s2, tpr, s_red[0]);
+    rstd = 1.0f / sqrtf(s2[0] / (float)p.cols + p.eps);
+  }
+  if (threadIdx.x == 0) {
+    if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
+    if (p.rstd != nullptr) p.rstd[row] = rstd;
+  }
+  const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
+  const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
+  TO* __restrict__ yr = reinterpret_cast<TO*>(p.y) + base;
+  for (int j = threadIdx.x; j < p.cols; j += blockDim.x) {
+    float s = load_s(j);
+    if (sr != nullptr) sr[j] = Cvt<TI>::from_f(s);
+    float v = (s - mean) * rstd;
+    if (gp != nullptr) v *= Cvt<TI>::to_f(gp[j]);
+    if (bp != nullptr) v += Cvt<TI>::to_f(bp[j]);
+    yr[j] = Cvt<TO>::from_f(apply_act<ACT>(v));
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// dispatch
+// ----------------------------------------------------------------------------------------
+template <typename TI, typename TO, int VEC, int KIND, int ACT>
+static int launch_k(const FwdParams& p, const Plan& pl, int64_t grid, cudaStream_t st) {
+  switch (pl.K) {
+    case 1:
+      norm_fwd_kernel<TI, TO, VEC, 1, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      break;
+    case 2:
+      norm_fwd_kernel<TI, TO, VEC, 2, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      break;
+    case 4:
+      norm_fwd_kernel<TI, TO, VEC, 4, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      break;
+    case 8:
+      norm_fwd_kernel<TI, TO, VEC, 8, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      break;
+    default:
+      return FLN_ERR_ARG;
+  }
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
+}
+
+template <typename TI, typename TO, int KIND, int ACT>
+static int launch_typed(FwdParams p, bool aligned, cudaStream_t st) {
+  constexpr int FULL = 16 / (sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO));
+  // a vector of the wider type must still be <= 16 bytes; alignment of the narrower
+  // type's rows follows from cols % FULL == 0 only when its pointer is aligned as well,
+  // which `aligned` asserts for every matrix pointer at 16 bytes.
+  Plan pl = make_plan(false, p.rows, p.cols, (int)(16 / FULL), aligned);
+  p.tpr = pl.tpr;
+  p.log2_tpr = pl.log2_tpr;
+  if (pl.generic) {
+    norm_fwd_generic_kernel<TI, TO, KIND, ACT><<<(unsigned)p.rows, 512, 0, st>>>(p);
+    FLN_CHECK_LAUNCH();
+    return FLN_OK;
+  }
+  p.nv = p.cols / pl.vec;
+  const int64_t grid = (p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta;
+  if (pl.vec == FULL) return launch_k<TI, TO, FULL, KIND, ACT>(p, pl, grid, st);
+  return launch_k<TI, TO, 1, KIND, ACT>(p, pl, grid, st);
+}
+
+template <typename TI, typename TO>
+static int launch_kind_act(int kind, int act, const FwdParams& p, bool aligned, cudaStream_t st) {
+  if (kind == FLN_RMSNORM) {
+    if (act != FLN_ACT_NONE) return FLN_ERR_UNSUPPORTED;
+    return launch_typed<TI, TO, FLN_RMSNORM, FLN_ACT_NONE>(p, aligned, st);
+  }
+  switch (act) {
+    case FLN_ACT_NONE:
+      return launch_typed<TI, TO, FLN_LAYERNORM, FLN_ACT_NONE>(p, aligned, st);
+    case FLN_ACT_GELU_TANH:
+      return launch_typed<TI, TO, FLN_LAYERNORM, FLN_ACT_GELU_TANH>(p, aligned, st);
+    case FLN_ACT_GELU_ERF:
+      return launch_typed<TI, TO, FLN_LAYERNORM, FLN_ACT_GELU_ERF>(p, aligned, st);
+  }
+  return FLN_ERR_ARG;
+}
+
+}  // namespace fln
+
+using namespace fln;
+
+extern "C" int fln_norm_forward(int kind, const void* x, const void* residual, const void* gamma,
+                                const void* beta, void* y, void* sum_out, float* mean,
+                                float* rstd, int64_t rows, int64_t cols, int io_dtype,
+                                int out_dtype, float eps, int act, void* stream) {
+  if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
+  if (act < FLN_ACT_NONE || act > FLN_ACT_GELU_ERF) return FLN_ERR_ARG;
+  if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
+  if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
+  if (out_dtype != io_dtype && !(io_dtype == FLN_F32 && out_dtype == FLN_BF16)) return FLN_ERR_DTYPE;
+  if (rows == 0) return FLN_OK;
+  if (x == nullptr || y == nullptr) return FLN_ERR_NULL;
+  if (residual != nullptr && sum_out == nullptr) return FLN_ERR_NULL;
+  if (kind == FLN_RMSNORM && (beta != nullptr || mean != nullptr)) return FLN_ERR_ARG;
+
+  FwdParams p;
+  p.x = x;
+  p.res = residual;
+  p.gamma = gamma;
+  p.beta = beta;
+  p.y = y;
+  p.sum_out = sum_out;
+  p.mean = mean;
+  p.rstd = rstd;
+  p.rows = rows;
+  p.cols = (int)cols;
+  p.nv = 0;
+  p.tpr = 0;
+  p.log2_tpr = 0;
+  p.eps = eps;
+  const bool aligned = is_aligned16(x) && is_aligned16(y) && is_aligned16(residual) &&
+                       is_aligned16(sum_out) && is_aligned16(gamma) && is_aligned16(beta);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (io_dtype == FLN_F32 && out_dtype == FLN_F32)
+    return launch_kind_act<float, float>(kind, act, p, aligned, st);
+  if (io_dtype == FLN_F32 && out_dtype == FLN_BF16)
+    return launch_kind_act<float, __nv_bfloat16>(kind, act, p, aligned, st);
+  if (io_dtype == FLN_BF16)
+    return launch_kind_act<__nv_bfloat16, __nv_bfloat16>(kind, act, p, aligned, st);
+  return launch_kind_act<__half, __half>(kind, act, p, aligned, st);
+}
+
+extern "C" int fln_layernorm_forward(const void* x, const void* gamma, const void* beta, void* y,
+                                     float* mean, float* rstd, int64_t rows, int64_t cols,
+                                     int dtype, float eps, void* stream) {
+  return fln_norm_forward(FLN_LAYERNORM, x, nullptr, gamma, beta, y, nullptr, mean, rstd, rows,
+                          cols, dtype, dtype, eps, FLN_ACT_NONE, stream);
+}
+
+extern "C" int fln_layernorm_gelu_forward(const void* x, const void* gamma, const void* beta,
+                                          void* y, int64_t rows, int64_t cols, int dtype,
+                                          float eps, int approximate, void* stream) {
+  if (approximate != FLN_ACT_GELU_TANH && approximate != FLN_ACT_GELU_ERF) return FLN_ERR_ARG;
+  return fln_norm_forward(FLN_LAYERNORM, x, nullptr, gamma, beta, y, nullptr, nullptr, nullptr,
+                          rows, cols, dtype, dtype, eps, approximate, stream);
+}

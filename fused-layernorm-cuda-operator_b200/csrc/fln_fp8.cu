@@ -1,0 +1,306 @@
+// (residual +) LayerNorm / RMSNorm forward with fp8-e4m3 output and a per-tensor scale
+// computed on the device, for sm_100a.
+//
+// The scale depends on amax over the whole tensor, so the work is two launches:
+//   phase 1  norm_amax_kernel: read x (+ residual) once, write the bf16/f16/f32 sum s and
+//            the per-row statistics, reduce max|y| per CTA and fold it into *amax with
+//            one atomicMax per CTA (non-negative floats order like their bit patterns);
+//   phase 2  norm_quant_kernel: re-read s, recompute y, store sat_e4m3(y * 448/amax).
+//            Rows are walked from the last to the first so the rows phase 1 wrote most
+//            recently are still in L2.
+// There is no grid-wide wait anywhere.  The reference has no counterpart.
+#include "fln_common.cuh"
+
+namespace fln {
+
+struct Fp8Params {
+  const void* x;
+  const void* res;
+  const void* gamma;
+  const void* beta;
+  void* q;
+  void* sum_out;
+  float* mean;
+  float* rstd;
+  float* amax;
+  float* scale;
+  int64_t rows;
+  int cols;
+  int nv;
+  int tpr;
+  int log2_tpr;
+  float eps;
+};
+
+template <int K>
+struct Fp8MaxThreads {
+  static constexpr int value = K <= 2 ? 1024 : 512;
+};
+
+template <typename TI, int VEC, int K, int KIND>
+__global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(const Fp8Params p) {
+  __shared__ float s_red[96];
+  __shared__ float s_max[32];
+
+  const int tid = threadIdx.x;
+  const int tpr = p.tpr;
+  const int lane_r = tid & (tpr - 1);
+  const int row_in_cta = tid >> p.log2_tpr;
+  const int rows_per_cta = blockDim.x >> p.log2_tpr;
+  const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
+  const bool row_ok = row < p.rows;
+  const int64_t base = row * (int64_t)p.cols;
+  const TI* __restrict__ xr = reinterpret_cast<const TI*>(p.x) + base;
+
+  Pack<TI, VEC> raw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (row_ok && iv < p.nv) {
+      raw[k] = ld_stream<TI, VEC>(xr + (int64_t)iv * VEC);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) raw[k].e[i] = Cvt<TI>::from_f(0.f);
+    }
+  }
+  if (p.res != nullptr) {
+    const TI* __restrict__ rr = reinterpret_cast<const TI*>(p.res) + base;
+    TI* __restrict__ sr = reinterpret_cast<TI*>(p.sum_out) + base;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (row_ok && iv < p.nv) {
+        Pack<TI, VEC> r = ld_stream<TI, VEC>(rr + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          raw[k].e[i] = Cvt<TI>::from_f(Cvt<TI>::to_f(raw[k].e[i]) + Cvt<TI>::to_f(r.e[i]));
+        // plain store: phase 2 wants to find these lines in L2
+        st_plain<TI, VEC>(sr + (int64_t)iv * VEC, raw[k]);
+      }
+    }
+  }
+
+  float mean = 0.f, rstd;
+  if (KIND == FLN_LAYERNORM) {
+    float lsum = 0.f, cnt = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (iv < p.nv) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) lsum += Cvt<TI>::to_f(raw[k].e[i]);
+        cnt += (float)VEC;
+      }
+    }
+    Wf w;
+    w.n = cnt;
+    w.mean = cnt > 0.f ? lsum / cnt : 0.f;
+    w.m2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (iv < p.nv) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          float d = Cvt<TI>::to_f(raw[k].e[i]) - w.mean;
+          w.m2 += d * d;
+        }
+      }
+    }
+    w = group_reduce_wf(w, tpr, s_red);
+    mean = w.mean;
+    rstd = 1.0f / sqrtf(w.m2 / (float)p.cols + p.eps);
+  } else {
+    float ss[1] = {0.f};
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float v = Cvt<TI>::to_f(raw[k].e[i]);
+        ss[0] += v * v;
+      }
+    }
+    group_reduce_sum<1>(ss, tpr, s_red);
+    rstd = 1.0f / sqrtf(ss[0] / (float)p.cols + p.eps);
+  }
+  if (row_ok && lane_r == 0) {
+    if (KIND == FLN_LAYERNORM) p.mean[row] = mean;
+    p.rstd[row] = rstd;
+  }
+
+  const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
+  const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (row_ok && iv < p.nv) {
+      float v[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
+      if (gp != nullptr) {
+        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
+      }
+      if (bp != nullptr) {
+        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(v[i]));  // fmaxf drops NaN
+    }
+  }
+  // CTA-wide max, then one atomic per CTA
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const int lane = tid & 31, warp = tid >> 5;
+  if (lane == 0) s_max[warp] = amax;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float m = lane < nw ? s_max[lane] : 0.f;
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(m));
+  }
+}
+
+template <typename TI, int VEC, int K, int KIND>
+__global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(const Fp8Params p) {
+  const int tid = threadIdx.x;
+  const int tpr = p.tpr;
+  const int lane_r = tid & (tpr - 1);
+  const int row_in_cta = tid >> p.log2_tpr;
+  const int rows_per_cta = blockDim.x >> p.log2_tpr;
+  // last rows first
+  const int64_t row = p.rows - 1 - ((int64_t)blockIdx.x * rows_per_cta + row_in_cta);
+  if (row < 0) return;
+  const int64_t base = row * (int64_t)p.cols;
+  const TI* __restrict__ sr =
+      reinterpret_cast<const TI*>(p.res != nullptr ? p.sum_out : p.x) + base;
+
+  Pack<TI, VEC> raw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (iv < p.nv) raw[k] = ld_stream<TI, VEC>(sr + (int64_t)iv * VEC);
+  }
+  const float am = *p.amax;
+  const float scale = am > 0.f ? 448.0f / am : 1.0f;
+  if (blockIdx.x == 0 && tid == 0) *p.scale = scale;
+  const float mean = KIND == FLN_LAYERNORM ? p.mean[row] : 0.f;
+  const float rstd = p.rstd[row];
+
+  const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
+  const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
+  unsigned char* __restrict__ qr = reinterpret_cast<unsigned char*>(p.q) + base;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    if (iv < p.nv) {
+      float v[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
+      if (gp != nullptr) {
+        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
+      }
+      if (bp != nullptr) {
+        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
+      }
+      Pack<unsigned char, VEC> o;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i)
+        o.e[i] = (unsigned char)__nv_cvt_float_to_fp8(v[i] * scale, __NV_SATFINITE, __NV_E4M3);
+      st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, o);
+    }
+  }
+}
+
+template <typename TI, int KIND>
+static int run_fp8(Fp8Params p, cudaStream_t st) {
+  constexpr int FULL = 16 / sizeof(TI);
+  Plan pl = make_plan(false, p.rows, p.cols, (int)sizeof(TI), true);
+  if (pl.generic || pl.vec != FULL) return FLN_ERR_UNSUPPORTED;
+  p.tpr = pl.tpr;
+  p.log2_tpr = pl.log2_tpr;
+  p.nv = p.cols / FULL;
+  const unsigned grid = (unsigned)((p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta);
+  if (cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+#define FLN_FP8_CASE(KK)                                                       \
+  case KK:                                                                     \
+    norm_amax_kernel<TI, FULL, KK, KIND><<<grid, pl.threads, 0, st>>>(p);      \
+    norm_quant_kernel<TI, FULL, KK, KIND><<<grid, pl.threads, 0, st>>>(p);     \
+    break;
+  switch (pl.K) {
+    FLN_FP8_CASE(1)
+    FLN_FP8_CASE(2)
+    FLN_FP8_CASE(4)
+    FLN_FP8_CASE(8)
+    default:
+      return FLN_ERR_ARG;
+  }
+#undef FLN_FP8_CASE
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
+}
+
+}  // namespace fln
+
+using namespace fln;
+
+extern "C" int fln_norm_forward_fp8(int kind, const void* x, const void* residual,
+                                    const void* gamma, const void* beta, void* q, void* sum_out,
+                                    float* mean, float* rstd, float* amax, float* scale,
+                                    int64_t rows, int64_t cols, int io_dtype, float eps,
+                                    void* stream) {
+  if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
+  if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
+  if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
+  if (amax == nullptr || scale == nullptr) return FLN_ERR_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    // empty tensor: amax = 0, scale = 1
+    const float one = 1.0f;
+    if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+    if (cudaMemcpyAsync(scale, &one, sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
+      return FLN_ERR_LAUNCH;
+    return FLN_OK;
+  }
+  if (x == nullptr || q == nullptr || rstd == nullptr) return FLN_ERR_NULL;
+  if (residual != nullptr && sum_out == nullptr) return FLN_ERR_NULL;
+  if (kind == FLN_LAYERNORM && mean == nullptr) return FLN_ERR_NULL;
+  if (kind == FLN_RMSNORM && (beta != nullptr || mean != nullptr)) return FLN_ERR_ARG;
+  const int es = io_dtype == FLN_F32 ? 4 : 2;
+  if (cols % (16 / es) != 0) return FLN_ERR_UNSUPPORTED;
+  if (!(is_aligned16(x) && is_aligned16(residual) && is_aligned16(sum_out) && is_aligned16(q) &&
+        is_aligned16(gamma) && is_aligned16(beta)))
+    return FLN_ERR_UNSUPPORTED;
+
+  Fp8Params p;
+  p.x = x;
+  p.res = residual;
+  p.gamma = gamma;
+  p.beta = beta;
+  p.q = q;
+  p.sum_out = sum_out;
+  p.mean = mean;
+  p.rstd = rstd;
+  p.amax = amax;
+  p.scale = scale;
+  p.rows = rows;
+  p.cols = (int)cols;
+  p.nv = 0;
+  p.tpr = 0;
+  p.log2_tpr = 0;
+  p.eps = eps;
+#define FLN_RUN(T) \
+  (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, st) : run_fp8<T, FLN_RMSNORM>(p, st))
+  if (io_dtype == FLN_F32) return FLN_RUN(float);
+  if (io_dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
+  return FLN_RUN(__half);
+#undef FLN_RUN
+}

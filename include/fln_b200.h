@@ -1,0 +1,205 @@
+/*
+ * fln_b200.h -- C ABI of the B200 (sm_100a) row-normalization library, libfln_b200.so.
+ *
+ * Every entry point takes plain device pointers, sizes and enums; nothing here depends
+ * on PyTorch.  Unless stated otherwise an entry point
+ *   - launches asynchronously on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) of the CUDA device that is current on the calling thread,
+ *   - allocates nothing: the caller owns inputs, outputs and scratch,
+ *   - returns FLN_OK (0) or one of the fln_status codes below and never aborts.
+ * Matrices are row-major and contiguous: `rows` x `cols`, row pitch == cols.
+ *
+ * Each declaration names the interface of the reference project
+ * (JonSnow1807/Fused-LayerNorm-CUDA-Operator, paths relative to its root) it stands in for.
+ */
+#ifndef FLN_B200_H
+#define FLN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of matrices and parameters */
+typedef enum {
+  FLN_F32 = 0,
+  FLN_BF16 = 1,
+  FLN_F16 = 2,
+  FLN_FP8_E4M3 = 3 /* output only */
+} fln_dtype;
+
+typedef enum { FLN_LAYERNORM = 0, FLN_RMSNORM = 1 } fln_kind;
+
+/* epilogue applied to the normalized value before it is stored.
+ * FLN_ACT_GELU_TANH is the reference's formula (csrc/layernorm_cuda_kernel.cu:31-36). */
+typedef enum { FLN_ACT_NONE = 0, FLN_ACT_GELU_TANH = 1, FLN_ACT_GELU_ERF = 2 } fln_act;
+
+typedef enum {
+  FLN_OK = 0,
+  FLN_ERR_DTYPE = 1,       /* dtype not supported by this entry point            */
+  FLN_ERR_SHAPE = 2,       /* rows < 0, cols <= 0, or cols beyond the int range  */
+  FLN_ERR_NULL = 3,        /* a required pointer is NULL                         */
+  FLN_ERR_WORKSPACE = 4,   /* scratch buffer missing or too small                */
+  FLN_ERR_LAUNCH = 5,      /* the CUDA runtime reported an error at launch       */
+  FLN_ERR_UNSUPPORTED = 6, /* combination not implemented (e.g. fp8 with odd cols) */
+  FLN_ERR_GRAPH = 7,       /* CUDA-graph capture / instantiate / launch failed   */
+  FLN_ERR_ARG = 8          /* bad enum value or inconsistent arguments           */
+} fln_status;
+
+/* Human-readable text for a status code (static storage). */
+const char* fln_status_string(int status);
+/* Library version "major.minor.patch" and the CUDA runtime it was built against.
+ * Stand in for the module attributes __version__ / __cuda_version__
+ * (csrc/layernorm_cuda.cpp:230-237). */
+const char* fln_version(void);
+int fln_cuda_runtime_version(void);
+
+/* ----------------------------------------------------------------------------------
+ * Forward
+ * -------------------------------------------------------------------------------- */
+
+/* y = (x - mean) * rstd * gamma + beta, per row; statistics in fp32.
+ * gamma and beta may each be NULL (treated as 1 and 0; the reference applies the affine
+ * only when both are present, csrc/layernorm_cuda_kernel.cu:87).  mean / rstd ([rows],
+ * fp32) may be NULL when the caller does not need them.
+ * Replaces layernorm_cuda (csrc/layernorm_cuda_kernel.cu:152-178, called from
+ * csrc/bindings.cpp:19-28) and layernorm_forward_cuda / layernorm_forward_cuda_optimized
+ * (declared csrc/layernorm_cuda.cpp:14-31, csrc/layernorm.h:15-22; defined
+ * csrc/layernorm_cuda_kernel_optimized.cu:171-212). */
+int fln_layernorm_forward(const void* x, const void* gamma, const void* beta, void* y,
+                          float* mean, float* rstd, int64_t rows, int64_t cols, int dtype,
+                          float eps, void* stream);
+
+/* y = gelu(layernorm(x)); `approximate` is FLN_ACT_GELU_TANH (the reference's formula)
+ * or FLN_ACT_GELU_ERF.  Replaces layernorm_gelu_cuda
+ * (csrc/layernorm_cuda_kernel.cu:180-206, called from csrc/bindings.cpp:30-39). */
+int fln_layernorm_gelu_forward(const void* x, const void* gamma, const void* beta, void* y,
+                               int64_t rows, int64_t cols, int dtype, float eps,
+                               int approximate, void* stream);
+
+/* General forward.  s = x (+ residual, rounded to io_dtype and written to sum_out when
+ * residual != NULL); y = act(norm(s)) stored as out_dtype.
+ *   kind      FLN_LAYERNORM (writes mean and rstd) or FLN_RMSNORM (writes rstd only;
+ *             beta and mean must be NULL)
+ *   io_dtype  type of x, residual, sum_out, gamma, beta: F32 / BF16 / F16
+ *   out_dtype type of y: io_dtype, or FLN_BF16 when io_dtype is FLN_F32
+ * No counterpart in the reference beyond the two entry points above; this is the fused
+ * residual-add / RMSNorm / down-cast variant of the same row kernel. */
+int fln_norm_forward(int kind, const void* x, const void* residual, const void* gamma,
+                     const void* beta, void* y, void* sum_out, float* mean, float* rstd,
+                     int64_t rows, int64_t cols, int io_dtype, int out_dtype, float eps,
+                     int act, void* stream);
+
+/* Forward with fp8-e4m3 output and a per-tensor scale computed on the device.
+ * Phase 1 reads x (+ residual), writes sum_out, mean/rstd, and reduces amax = max|y|
+ * over the whole tensor; phase 2 re-reads s and writes q = sat_e4m3(y * scale) with
+ * scale = 448 / amax (1 when amax == 0).  Two launches and one 4-byte memset, all on
+ * `stream`; there is no grid-wide wait.
+ *   q        [rows, cols] bytes (e4m3 codes)
+ *   sum_out  [rows, cols] io_dtype; required when residual != NULL, else may be NULL
+ *   mean     [rows] fp32, required for FLN_LAYERNORM, must be NULL for FLN_RMSNORM
+ *   rstd     [rows] fp32, required (phase 2 reads it)
+ *   amax, scale  one fp32 each, required
+ * cols must be a multiple of 16 / sizeof(io element) and every matrix pointer 16-byte
+ * aligned, otherwise FLN_ERR_UNSUPPORTED.  No counterpart in the reference. */
+int fln_norm_forward_fp8(int kind, const void* x, const void* residual, const void* gamma,
+                         const void* beta, void* q, void* sum_out, float* mean, float* rstd,
+                         float* amax, float* scale, int64_t rows, int64_t cols, int io_dtype,
+                         float eps, void* stream);
+
+/* ----------------------------------------------------------------------------------
+ * Backward
+ * -------------------------------------------------------------------------------- */
+
+/* Bytes of scratch fln_*_backward needs for this problem on the current device
+ * (per-CTA fp32 partial sums of dgamma/dbeta).  0 when rows == 0. */
+size_t fln_backward_workspace_bytes(int64_t rows, int64_t cols, int dtype);
+
+/* dx, dgamma, dbeta of LayerNorm from the saved per-row mean / rstd.
+ *   xhat = (x - mean) * rstd, g = dy * gamma
+ *   dx = rstd * (g - mean_j(g) - xhat * mean_j(g * xhat))
+ *   dgamma = sum_i dy * xhat,  dbeta = sum_i dy      (fp32 accumulation, fixed order)
+ * dx, dgamma, dbeta may each be NULL (that gradient is skipped); gamma may be NULL (== 1).
+ * `workspace` must hold fln_backward_workspace_bytes() bytes whenever dgamma or dbeta is
+ * requested.  Replaces layernorm_backward_cuda, which the reference declares
+ * (csrc/layernorm.h:24-32, csrc/layernorm_cuda.cpp:33-41) and calls
+ * (csrc/layernorm_cuda.cpp:135-138) but never defines. */
+int fln_layernorm_backward(const void* dy, const void* x, const float* mean,
+                           const float* rstd, const void* gamma, void* dx, void* dgamma,
+                           void* dbeta, void* workspace, size_t workspace_bytes,
+                           int64_t rows, int64_t cols, int dtype, void* stream);
+
+/* General backward.
+ *   kind      FLN_LAYERNORM or FLN_RMSNORM (mean, dbeta ignored / must be NULL)
+ *   x         the tensor that was normalized (s = x + residual for the fused-add forward)
+ *   dres_in   optional [rows, cols] gradient arriving on the residual stream; added to dx
+ *   dgb_f32   optional fp32 [2*cols] buffer receiving [dgamma | dbeta] unrounded (the
+ *             buffer a row-sharded job all-reduces); [cols] for FLN_RMSNORM
+ * No counterpart in the reference. */
+int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean,
+                      const float* rstd, const void* gamma, const void* dres_in, void* dx,
+                      void* dgamma, void* dbeta, float* dgb_f32, void* workspace,
+                      size_t workspace_bytes, int64_t rows, int64_t cols, int dtype,
+                      void* stream);
+
+/* dst[i] = (dtype) src[i] for n fp32 values: turns an all-reduced dgb_f32 buffer into
+ * parameter-typed gradients.  No counterpart in the reference. */
+int fln_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, void* stream);
+
+/* ----------------------------------------------------------------------------------
+ * CUDA-graph launch path for latency-bound shapes
+ * -------------------------------------------------------------------------------- */
+
+/* Record any sequence of fln_* launches once and replay it with one graph launch.
+ *   fln_graph_begin   creates a private stream and starts capturing on it
+ *   fln_graph_stream  the stream to pass to the fln_* calls being recorded
+ *   fln_graph_end     ends the capture and instantiates the graph
+ *   fln_graph_launch  replays on `stream`; pointers and sizes are those recorded
+ *   fln_graph_destroy releases everything (also valid after a failed end)
+ * The reference launches eagerly on the legacy stream only
+ * (csrc/layernorm_cuda_kernel.cu:171,199); it has no counterpart. */
+typedef struct fln_graph fln_graph;
+int fln_graph_begin(fln_graph** out);
+void* fln_graph_stream(fln_graph* g);
+int fln_graph_end(fln_graph* g);
+int fln_graph_launch(fln_graph* g, void* stream);
+int fln_graph_destroy(fln_graph* g);
+
+/* ----------------------------------------------------------------------------------
+ * Host-side helpers
+ * -------------------------------------------------------------------------------- */
+
+/* Closed-form byte estimate of a forward+backward call; same formula as
+ * get_memory_usage (csrc/layernorm_cuda.cpp:144-164). */
+int64_t fln_get_memory_usage(int batch_size, int hidden_size, int use_mixed_precision);
+
+/* Writes newline-separated advisory text into buf (always NUL-terminated) and returns the
+ * length that was needed.  Same messages as get_performance_hints
+ * (csrc/layernorm_cuda.cpp:167-195) but the SM count is queried, not assumed. */
+int fln_get_performance_hints(int batch_size, int hidden_size, char* buf, size_t buf_len);
+
+/* How a forward / backward call of this shape is launched on the current device. */
+typedef struct {
+  int generic;       /* 1: looping fallback kernel (row too long or ragged for registers) */
+  int vec_elems;     /* elements per vector load (1 = scalar path)                        */
+  int vecs_per_thread;
+  int threads_per_row;
+  int threads_per_cta;
+  int rows_per_cta;
+  int64_t grid;      /* CTAs launched                                                     */
+  int sm_count;
+} fln_launch_info;
+int fln_describe_launch(int backward, int64_t rows, int64_t cols, int dtype, int aligned16,
+                        fln_launch_info* out);
+
+/* Tuning hook: force vectors-per-thread (1,2,4,8) and threads-per-row (power of two,
+ * 8..1024) for subsequent launches of this process; 0 restores automatic selection.
+ * Combinations that cannot hold a row fall back to automatic selection. */
+void fln_set_plan_override(int vecs_per_thread, int threads_per_row);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLN_B200_H */
