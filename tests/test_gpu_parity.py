@@ -1,0 +1,414 @@
+"""GPU parity: the sm_100a kernels, called through the C ABI (ctypes), against the CPU oracle
+on identical seeded inputs.
+
+Tolerances (written where they are applied, gpu_util.assert_out_close):
+  fp32 outputs 1e-5 abs/rel; bf16 / fp16 outputs at most 1 unit in the last place; fp8 codes at
+  most one code step on at most 0.01 % of elements; saved mean / rstd 1e-5 rel.
+Shapes are the union of the reference's own test shapes (tests/test_layernorm.py:37-46,72-77,
+128-132,340-358; tests/edge_cases.py:12-23; tests/publication_validation.py:322-331 of the
+reference) and the benchmark configurations.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import gpu_util as U
+    from fused_layernorm import _capi as capi
+
+F32, BF16, F16 = torch.float32, torch.bfloat16, torch.float16
+
+REF_FWD_SHAPES = [(1, 768), (8, 768), (32, 768), (32, 1024), (64, 2048), (128, 4096)]
+EDGE_SHAPES = [(1, 1), (1, 17), (1000, 1), (1, 100000), (512, 512), (1, 32767), (1, 65536), (13, 13),
+               (1, 4095), (1, 4097), (32, 1), (2, 16384), (1, 32768), (3, 12288), (5, 8192), (7, 5120)]
+C2_SHAPES = [(32, 1024), (32, 4096), (64, 4096), (17, 1023)]
+
+
+def _seed(rows, cols):
+    return 20240 + (rows * 131 + cols) % 1000
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("shape", REF_FWD_SHAPES + EDGE_SHAPES)
+def test_layernorm_forward(shape, dtype):
+    rows, cols = shape
+    x, gamma, beta, _, _ = U.make_inputs(_seed(rows, cols), rows, cols, dtype)
+    got = U.run_forward(x, gamma, beta)
+    want = O.norm_forward(x, gamma, beta)
+    U.assert_out_close(got["y"], want["y"], dtype)
+    torch.testing.assert_close(got["mean"], want["mean"], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("act", ["none", "gelu_tanh", "gelu_erf"])
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("shape", C2_SHAPES)
+def test_c2_sweep_layernorm_and_gelu(shape, dtype, act):
+    rows, cols = shape
+    x, gamma, beta, _, _ = U.make_inputs(20242, rows, cols, dtype, x_scale=3.0, x_shift=0.5)
+    got = U.run_forward(x, gamma, beta, act=act, want_stats=False)
+    want = O.norm_forward(x, gamma, beta, act=act)
+    U.assert_out_close(got["y"], want["y"], dtype)
+
+
+def test_gelu_entry_point_defaults_to_reference_tanh_formula():
+    x, gamma, beta, _, _ = U.make_inputs(1, 32, 4096, F32)
+    y = torch.empty(32, 4096, device="cuda")
+    capi.layernorm_gelu_forward(x.cuda(), gamma.cuda(), beta.cuda(), y, 1e-5)
+    want = O.ref_g2_layernorm(x, gamma, beta, 1e-5, gelu=True)  # literal restatement of the shipped kernel
+    torch.testing.assert_close(y.cpu(), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("affine", ["none", "gamma_only", "beta_only"])
+def test_optional_affine(affine):
+    x, gamma, beta, _, _ = U.make_inputs(3, 16, 768, F32)
+    g = gamma if affine == "gamma_only" else None
+    b = beta if affine == "beta_only" else None
+    got = U.run_forward(x, g, b)
+    want = O.norm_forward(x, g, b)
+    U.assert_out_close(got["y"], want["y"], F32)
+
+
+@pytest.mark.parametrize("eps", [1e-5, 1e-6, 1e-7, 1e-8, 1e-12])
+def test_eps_values(eps):
+    x, gamma, beta, _, _ = U.make_inputs(4, 16, 768, F32)
+    got = U.run_forward(x, gamma, beta, eps=eps)
+    want = O.norm_forward(x, gamma, beta, eps=eps)
+    U.assert_out_close(got["y"], want["y"], F32)
+
+
+def test_numerical_stability_rows(golden):
+    x = torch.from_numpy(golden.raw("stability/x").copy())
+    got = U.run_forward(x, None, None)["y"]
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, torch.from_numpy(golden.raw("stability/y").copy()), rtol=1e-3, atol=1e-3)
+    # a constant row has zero variance: the output must be exactly beta (here 0)
+    assert float(got[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("scale", [1000.0, 1e-3, 1e-6])
+def test_value_ranges_32x4096(scale):
+    x, gamma, beta, _, _ = U.make_inputs(5, 32, 4096, F32, x_scale=scale)
+    got = U.run_forward(x, gamma, beta)
+    want = O.norm_forward(x, gamma, beta)
+    torch.testing.assert_close(got["y"], want["y"], rtol=1e-4, atol=1e-5)
+
+
+def test_bitwise_determinism():
+    for seed in range(5):
+        x, gamma, beta, dy, _ = U.make_inputs(seed, 32, 768, F32)
+        a = U.run_forward(x, gamma, beta)
+        b = U.run_forward(x, gamma, beta)
+        assert torch.equal(a["y"], b["y"])
+        ga = U.run_backward(dy, x, a["mean"], a["rstd"], gamma)
+        gb = U.run_backward(dy, x, a["mean"], a["rstd"], gamma)
+        for k in ("dx", "dgamma", "dbeta"):
+            assert torch.equal(ga[k], gb[k])
+
+
+@pytest.mark.parametrize("name", ["c1_ln_f32_32x768", "c2_ln_f32_5x1023", "c2_ln_bf16_5x1023",
+                                  "c2_ln_bf16_2x4096", "ln_f16_8x256", "c3_addln_bf16_8x512",
+                                  "rms_f32_8x384", "ln_f32_noaffine_5x13"])
+def test_against_golden_fixtures(golden, name):
+    c = golden.case(name)
+    got = U.run_forward(c["x"], c["gamma"], c["beta"], c["res"], c["kind"], c["eps"])
+    U.assert_out_close(got["y"], c["y"], c["dtype"])
+    torch.testing.assert_close(got["rstd"], c["rstd"], rtol=1e-5, atol=1e-5)
+    if c["res"] is not None:
+        assert torch.equal(got["sum"].view(torch.int16), c["sum"].view(torch.int16))
+    for act in ("gelu_tanh", "gelu_erf"):
+        if "y_" + act in c:
+            ga = U.run_forward(c["x"], c["gamma"], c["beta"], None, c["kind"], c["eps"], act)
+            U.assert_out_close(ga["y"], c["y_" + act], c["dtype"])
+    s = got["sum"] if c["res"] is not None else c["x"]
+    b = U.run_backward(c["dy"], s, got["mean"], got["rstd"], c["gamma"], c["kind"])
+    if c["dtype"] == F32:
+        torch.testing.assert_close(b["dx"], c["dx"], rtol=1e-4, atol=1e-4)  # reference grad tolerance
+    cols = s.shape[1]
+    if c["dgamma"] is not None:
+        torch.testing.assert_close(b["dgb_f32"][:cols], c["dgamma"], rtol=1e-4, atol=1e-4)
+    if c["kind"] == "layernorm" and c["dbeta"] is not None:
+        torch.testing.assert_close(b["dgb_f32"][cols:], c["dbeta"], rtol=1e-4, atol=1e-4)
+
+
+# ------------------------------------------------------------------------------------ backward
+BWD_SHAPES = [(16, 768), (32, 1024), (64, 2048), (17, 1023), (13, 13), (1, 1), (1000, 1), (3, 12288),
+              (2, 16384), (700, 4096), (333, 8192), (1, 100000), (1, 4097)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+def test_layernorm_backward(shape, dtype):
+    rows, cols = shape
+    x, gamma, beta, dy, _ = U.make_inputs(_seed(rows, cols) + 1, rows, cols, dtype)
+    f = O.norm_forward(x, gamma, beta)
+    got = U.run_backward(dy, x, f["mean"], f["rstd"], gamma)
+    want = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma)
+    if dtype == F32:
+        torch.testing.assert_close(got["dx"], want["dx32"], rtol=1e-5, atol=1e-5)
+    else:
+        U.assert_out_close(got["dx"], want["dx"], dtype)
+    U.assert_param_grads_close(got["dgb_f32"][:cols], want["dgamma64"], want["abs64"][0], rows)
+    U.assert_param_grads_close(got["dgb_f32"][cols:], want["dbeta64"], want["abs64"][1], rows)
+    # typed outputs are the single rounding of the fp32 sums
+    assert torch.equal(got["dgamma"], got["dgb_f32"][:cols].to(dtype))
+    assert torch.equal(got["dbeta"], got["dgb_f32"][cols:].to(dtype))
+
+
+@pytest.mark.parametrize("mask", [(True, False, False), (False, True, True), (True, True, False)])
+def test_backward_output_mask(mask):
+    x, gamma, beta, dy, _ = U.make_inputs(9, 48, 1024, F32)
+    f = O.norm_forward(x, gamma, beta)
+    full = U.run_backward(dy, x, f["mean"], f["rstd"], gamma)
+    got = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, want=mask, with_f32=False)
+    for k, m in zip(("dx", "dgamma", "dbeta"), mask):
+        if m:
+            assert torch.equal(got[k], full[k])
+        else:
+            assert got[k] is None
+
+
+def test_backward_without_gamma_and_with_incoming_residual_grad():
+    x, _, _, dy, res = U.make_inputs(10, 40, 2048, BF16, residual=True)
+    f = O.norm_forward(x, None, None)
+    got = U.run_backward(dy, x, f["mean"], f["rstd"], None, dres_in=res)
+    want = O.norm_backward(dy, x, f["mean"], f["rstd"], None, dres_in=res)
+    U.assert_out_close(got["dx"], want["dx"], BF16)
+
+
+def test_backward_workspace_is_checked():
+    x, gamma, beta, dy, _ = U.make_inputs(11, 64, 1024, F32)
+    f = O.norm_forward(x, gamma, beta)
+    dx = torch.empty(64, 1024, device="cuda")
+    dg = torch.empty(1024, device="cuda")
+    with pytest.raises(RuntimeError, match="workspace"):
+        capi.layernorm_backward(dy.cuda(), x.cuda(), f["mean"].cuda(), f["rstd"].cuda(), gamma.cuda(), dx, dg,
+                                None, None)
+
+
+# ------------------------------------------------------------------------- residual / rmsnorm
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("shape", [(64, 4096), (17, 1023), (130, 512), (9, 8192)])
+def test_residual_add_norm_forward_backward(shape, dtype, kind):
+    rows, cols = shape
+    x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 2, rows, cols, dtype, residual=True)
+    if kind == "rmsnorm":
+        beta = None
+    got = U.run_forward(x, gamma, beta, res, kind)
+    want = O.norm_forward(x, gamma, beta, res, kind)
+    assert torch.equal(got["sum"].view(torch.int16 if dtype != F32 else torch.int32),
+                       want["sum"].view(torch.int16 if dtype != F32 else torch.int32))
+    U.assert_out_close(got["y"], want["y"], dtype)
+    torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+    gb = U.run_backward(dy, want["sum"], want["mean"], want["rstd"], gamma, kind)
+    wb = O.norm_backward(dy, want["sum"], want["mean"], want["rstd"], gamma, None, kind)
+    if dtype == F32:
+        torch.testing.assert_close(gb["dx"], wb["dx32"], rtol=1e-5, atol=1e-5)
+    else:
+        U.assert_out_close(gb["dx"], wb["dx"], dtype)
+    U.assert_param_grads_close(gb["dgb_f32"][:cols], wb["dgamma64"], wb["abs64"][0], rows)
+
+
+def test_fp32_in_bf16_out():
+    x, gamma, beta, _, _ = U.make_inputs(12, 33, 2048, F32)
+    got = U.run_forward(x, gamma, beta, out_dtype=BF16)
+    want = O.norm_forward(x, gamma, beta, out_dtype=BF16)
+    U.assert_out_close(got["y"], want["y"], BF16)
+
+
+# ------------------------------------------------------------------------------------- fp8
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("rmsnorm", False), ("layernorm", True)])
+@pytest.mark.parametrize("dtype", [BF16, F16, F32])
+@pytest.mark.parametrize("shape", [(64, 8192), (257, 1024), (5, 4096)])
+def test_fp8_output(shape, dtype, kind, residual):
+    rows, cols = shape
+    x, gamma, beta, _, res = U.make_inputs(20244, rows, cols, dtype, residual=residual, outliers=True)
+    if kind == "rmsnorm":
+        beta = None
+    q = U.Guarded((rows, cols), torch.uint8)
+    s = U.Guarded((rows, cols), dtype) if residual else None
+    mean = torch.empty(rows, device="cuda") if kind == "layernorm" else None
+    rstd = torch.empty(rows, device="cuda")
+    amax = torch.full((1,), -1.0, device="cuda")
+    scale = torch.full((1,), -1.0, device="cuda")
+    capi.norm_forward_fp8(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t,
+                          s.t if s else None, mean, rstd, amax, scale, 1e-6)
+    torch.cuda.synchronize()
+    want = O.norm_forward(x, gamma, beta, res, kind, 1e-6)
+    wq, wamax, wscale = O.quant_fp8(want["y32"])
+    torch.testing.assert_close(amax.cpu(), wamax, rtol=1e-5, atol=0)
+    torch.testing.assert_close(scale.cpu(), wscale, rtol=1e-5, atol=0)
+    d = O.fp8_code_distance(q.check().cpu(), wq)
+    assert int(d.max()) <= 1
+    # on this few elements "0.01 %" may be less than one element; allow the larger of the two
+    assert int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+    if residual:
+        assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
+
+
+def test_fp8_golden_fixture(golden):
+    c = golden.case("c4_addrms_fp8_bf16_8x1024")
+    rows, cols = c["x"].shape
+    q = torch.empty(rows, cols, dtype=torch.uint8, device="cuda")
+    s = torch.empty(rows, cols, dtype=BF16, device="cuda")
+    rstd = torch.empty(rows, device="cuda")
+    amax = torch.zeros(1, device="cuda")
+    scale = torch.zeros(1, device="cuda")
+    capi.norm_forward_fp8(capi.RMSNORM, c["x"].cuda(), c["res"].cuda(), c["gamma"].cuda(), None, q, s, None,
+                          rstd, amax, scale, c["eps"])
+    torch.testing.assert_close(scale.cpu(), c["scale"], rtol=1e-5, atol=0)
+    d = O.fp8_code_distance(q.cpu(), c["q"])
+    assert int(d.max()) <= 1 and int((d > 0).sum()) <= 1
+    assert torch.equal(s.cpu().view(torch.int16), c["sum"].view(torch.int16))
+
+
+def test_fp8_rejects_ragged_rows():
+    x = torch.randn(4, 1023, device="cuda", dtype=BF16)
+    q = torch.empty(4, 1023, dtype=torch.uint8, device="cuda")
+    rstd = torch.empty(4, device="cuda")
+    amax = torch.zeros(1, device="cuda")
+    with pytest.raises(RuntimeError, match="unsupported"):
+        capi.norm_forward_fp8(capi.RMSNORM, x, None, None, None, q, None, None, rstd, amax, amax.clone(), 1e-6)
+
+
+# ------------------------------------------------------------------------- misc C-ABI behaviour
+def test_empty_input_is_a_no_op():
+    x = torch.empty(0, 768, device="cuda")
+    y = torch.empty(0, 768, device="cuda")
+    capi.layernorm_forward(x, None, None, y, None, None, 1e-5)
+    dg = torch.full((768,), 5.0, device="cuda")
+    capi.layernorm_backward(x, x, torch.empty(0, device="cuda"), torch.empty(0, device="cuda"), None, y, dg,
+                            None, None)
+    assert float(dg.abs().max()) == 0.0  # an empty shard contributes zeros
+
+
+def test_misaligned_pointers_take_the_scalar_path():
+    x, gamma, beta, _, _ = U.make_inputs(13, 8, 1024, BF16)
+    buf = torch.empty(8 * 1024 + 8, dtype=BF16, device="cuda")
+    xo = buf[1:1 + 8 * 1024].view(8, 1024)  # 2-byte aligned only
+    xo.copy_(x)
+    y = torch.empty(8, 1024, dtype=BF16, device="cuda")
+    capi.layernorm_forward(xo, gamma.cuda(), beta.cuda(), y, None, None, 1e-5)
+    U.assert_out_close(y.cpu(), O.norm_forward(x, gamma, beta)["y"], BF16)
+
+
+def test_graph_replay_matches_eager():
+    x, gamma, beta, _, _ = U.make_inputs(14, 32, 4096, F32)
+    xd, gd, bd = x.cuda(), gamma.cuda(), beta.cuda()
+    y_eager = torch.empty_like(xd)
+    capi.layernorm_forward(xd, gd, bd, y_eager, None, None, 1e-5)
+    y_graph = torch.zeros_like(xd)
+    g = capi.Graph()
+    with g.record() as s:
+        capi.layernorm_forward(xd, gd, bd, y_graph, None, None, 1e-5, stream=s)
+    torch.cuda.synchronize()
+    assert float(y_graph.abs().max()) == 0.0  # recording does not execute
+    for _ in range(3):
+        g.launch()
+    torch.cuda.synchronize()
+    assert torch.equal(y_graph, y_eager)
+    g.close()
+
+
+def test_describe_launch_reports_register_path_for_headline_shape():
+    info = capi.describe_launch(False, 16384, 8192, BF16)
+    assert info["generic"] == 0 and info["vec_elems"] == 8
+    assert info["vecs_per_thread"] * info["threads_per_row"] * info["vec_elems"] >= 8192
+    assert info["sm_count"] == torch.cuda.get_device_properties(0).multi_processor_count
+
+
+# ----------------------------------------------------------------- full benchmark sizes
+def _sampled_rows_check(x, y, gamma, beta, rows_idx, kind="layernorm", res=None, eps=1e-5):
+    xs = x[rows_idx].cpu()
+    rs = None if res is None else res[rows_idx].cpu()
+    want = O.norm_forward(xs, None if gamma is None else gamma.cpu(), None if beta is None else beta.cpu(), rs,
+                          kind, eps)
+    U.assert_out_close(y[rows_idx].cpu(), want["y"], x.dtype)
+    return want
+
+
+def test_headline_size_forward_backward_properties():
+    """16384 x 8192 bf16 (the headline configuration): sampled rows against the oracle, plus
+    size-independent properties: with gamma = 1, beta = 0 every output row has mean ~ 0 and
+    variance ~ 1; dx rows are orthogonal to 1 and to xhat; dbeta equals the column sums of dy."""
+    rows, cols = 16384, 8192
+    g = torch.Generator(device="cuda").manual_seed(20245)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(BF16)
+    dy = torch.randn(rows, cols, device="cuda", generator=g).to(BF16)
+    gamma = torch.ones(cols, dtype=BF16, device="cuda")
+    beta = torch.zeros(cols, dtype=BF16, device="cuda")
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, device="cuda")
+    rstd = torch.empty(rows, device="cuda")
+    capi.layernorm_forward(x, gamma, beta, y, mean, rstd, 1e-5)
+    idx = torch.tensor([0, 1, 147, 148, 8191, 8192, 12345, 16382, 16383], device="cuda")
+    _sampled_rows_check(x, y, gamma, beta, idx)
+    yf = y.float()
+    assert float(yf.mean(-1).abs().max()) < 2e-3           # bf16 rounding of 8192 values
+    assert float((yf.var(-1, unbiased=False) - 1).abs().max()) < 5e-3
+
+    dx = torch.empty_like(x)
+    dgb = torch.empty(2 * cols, device="cuda")
+    ws = torch.empty(capi.backward_workspace_bytes(rows, cols, BF16) // 4, device="cuda")
+    capi.norm_backward(capi.LAYERNORM, dy, x, mean, rstd, gamma, None, dx, None, None, dgb, ws)
+    want = O.norm_backward(dy[idx].cpu(), x[idx].cpu(), mean[idx].cpu(), rstd[idx].cpu(), gamma.cpu())
+    U.assert_out_close(dx[idx].cpu(), want["dx"], BF16)
+    dxf = dx.float()
+    assert float(dxf.sum(-1).abs().max()) < 0.5            # sum_j dx = 0 up to bf16 rounding of 8192 terms
+    xh = (x.float() - mean[:, None]) * rstd[:, None]
+    assert float((dxf * xh).sum(-1).abs().max()) < 1.0     # sum_j dx xhat = 0 likewise
+    ref_db = dy.double().sum(0)
+    ref_dg = (dy.double() * xh.double()).sum(0)
+    scale_b = dy.double().abs().sum(0)
+    scale_g = (dy.double() * xh.double()).abs().sum(0)
+    assert bool(((dgb[cols:].double() - ref_db).abs() <= 1e-5 * ref_db.abs() + 1e-5 + 4e-7 * scale_b).all())
+    assert bool(((dgb[:cols].double() - ref_dg).abs() <= 1e-5 * ref_dg.abs() + 1e-5 + 4e-7 * scale_g).all())
+
+
+def test_c3_size_residual_layernorm():
+    rows, cols = 16384, 4096
+    g = torch.Generator(device="cuda").manual_seed(20243)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(BF16)
+    res = (0.5 * torch.randn(rows, cols, device="cuda", generator=g)).to(BF16)
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).to(BF16)
+    beta = (0.1 * torch.randn(cols, device="cuda", generator=g)).to(BF16)
+    y, s = torch.empty_like(x), torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    capi.norm_forward(capi.LAYERNORM, x, res, gamma, beta, y, s, mean, rstd, 1e-5)
+    assert torch.equal(s, x + res)                          # the unfused add, bit for bit
+    idx = torch.tensor([0, 5, 4095, 9999, 16383], device="cuda")
+    _sampled_rows_check(x, y, gamma, beta, idx, res=res)
+
+
+def test_c4_size_residual_rmsnorm_fp8():
+    rows, cols = 32768, 8192
+    g = torch.Generator(device="cuda").manual_seed(20244)
+    x = torch.randn(rows, cols, device="cuda", generator=g)
+    x = torch.where(torch.rand(rows, cols, device="cuda", generator=g) < 0.001, x * 50, x).to(BF16)
+    res = (0.5 * torch.randn(rows, cols, device="cuda", generator=g)).to(BF16)
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).to(BF16)
+    q = torch.empty(rows, cols, dtype=torch.uint8, device="cuda")
+    s = torch.empty_like(x)
+    rstd = torch.empty(rows, device="cuda")
+    amax, scale = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    capi.norm_forward_fp8(capi.RMSNORM, x, res, gamma, None, q, s, None, rstd, amax, scale, 1e-6)
+    assert torch.equal(s, x + res)
+    # amax / scale against a torch recomputation on the device (fp32 math on the same s)
+    sf = s.float()
+    y32 = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+    torch.testing.assert_close(amax, y32.abs().max().reshape(1), rtol=1e-5, atol=0)
+    torch.testing.assert_close(scale, 448.0 / amax, rtol=1e-6, atol=0)
+    # sampled rows: codes against the oracle's quantizer using the device-computed scale
+    idx = torch.tensor([0, 1, 777, 16384, 32767], device="cuda")
+    want = O.norm_forward(x[idx].cpu(), gamma.cpu(), None, res[idx].cpu(), "rmsnorm", 1e-6)
+    wq = O.e4m3_encode(want["y32"] * scale.cpu())
+    d = O.fp8_code_distance(q[idx].cpu(), wq)
+    assert int(d.max()) <= 1 and int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+    # dequantized round trip stays within one fp8 step of y
+    deq = q[idx].view(torch.float8_e4m3fn).float().cpu() / scale.cpu()
+    assert bool(((deq - want["y32"]).abs() <= want["y32"].abs() * 0.0625 + 2.0 ** -9 / scale.cpu()).all())
