@@ -12,26 +12,12 @@
 // The reference declares this operation (layernorm_backward_cuda, csrc/layernorm.h:24-32)
 // and calls it (csrc/layernorm_cuda.cpp:135-138) but ships no kernel; its intended
 // semantics are those of torch autograd through nn.LayerNorm (tests/test_layernorm.py:128-178).
+#include <type_traits>
+
 #include "fln_common.cuh"
 
 namespace fln {
 
-struct BwdParams {
-  const void* dy;
-  const void* x;
-  const float* mean;
-  const float* rstd;
-  const void* gamma;
-  const void* dres_in;
-  void* dx;
-  float* partials;  // [P][2][cols] (LayerNorm) or [P][1][cols] (RMSNorm); may be NULL
-  int64_t rows;
-  int64_t row_groups;
-  int cols;
-  int nv;
-  int tpr;
-  int log2_tpr;
-};
 
 template <int C>  // columns per thread
 struct BwdMaxThreads {
@@ -41,7 +27,7 @@ struct BwdMaxThreads {
 template <typename T, int VEC, int K, int KIND>
 __global__ void __launch_bounds__(BwdMaxThreads<VEC * K>::value) norm_bwd_kernel(const BwdParams p) {
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
-  __shared__ float s_red[2][NR * 32];
+  __shared__ __align__(16) float s_red[2][NR * 32];
 
   const int tid = threadIdx.x;
   const int tpr = p.tpr;
@@ -99,22 +85,28 @@ __global__ void __launch_bounds__(BwdMaxThreads<VEC * K>::value) norm_bwd_kernel
 
     // xhat and dy as floats; padding lanes carry dy == 0 so they add nothing anywhere
     float xh[K][VEC], dyf[K][VEC];
-    float red[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) red[r] = 0.f;
+    float ra[2] = {0.f, 0.f}, rb[2] = {0.f, 0.f};  // two chains per sum
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      unpack<T, VEC>(rdy[k], dyf[k]);
+      unpack<T, VEC>(rx[k], xh[k]);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        dyf[k][i] = Cvt<T>::to_f(rdy[k].e[i]);
-        xh[k][i] = (Cvt<T>::to_f(rx[k].e[i]) - mean) * rstd;
-        float g = dyf[k][i] * gam[k][i];
-        red[0] += g * xh[k][i];
-        if (KIND == FLN_LAYERNORM) red[NR - 1] += g;
+        xh[k][i] = (xh[k][i] - mean) * rstd;
+        const float g = dyf[k][i] * gam[k][i];
+        ra[i & 1] = fmaf(g, xh[k][i], ra[i & 1]);
+        if (KIND == FLN_LAYERNORM) rb[i & 1] += g;
       }
     }
-    group_reduce_sum<NR>(red, tpr, s_red[parity]);
-    const float c1 = red[0] * inv_n;
+    float red[NR];
+    red[0] = ra[0] + ra[1];
+    if (KIND == FLN_LAYERNORM) red[NR - 1] = rb[0] + rb[1];
+    rowsum_warp<NR>(red, tpr, s_red[parity]);
+    if (tpr > 32) __syncthreads();
+    rowsum_cta<NR>(red, tpr, s_red[parity]);
+    // dx = rstd * ((g - c2) - xhat * c1): the subtraction comes first so that rows whose g
+    // is (nearly) constant cancel exactly instead of leaving a rounding residue times rstd
+    const float nc1 = -(red[0] * inv_n);
     const float c2 = KIND == FLN_LAYERNORM ? red[NR - 1] * inv_n : 0.f;
 
     if (p.dx != nullptr) {
@@ -127,18 +119,16 @@ __global__ void __launch_bounds__(BwdMaxThreads<VEC * K>::value) norm_bwd_kernel
         if (row_ok && iv < p.nv) {
           float o[VEC];
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) {
-            float g = dyf[k][i] * gam[k][i];
-            o[i] = rstd * (g - c2 - xh[k][i] * c1);
-          }
+          for (int i = 0; i < VEC; ++i)
+            o[i] = rstd * fmaf(xh[k][i], nc1, dyf[k][i] * gam[k][i] - c2);
           if (drr != nullptr) {
-            Pack<T, VEC> d = ld_stream<T, VEC>(drr + (int64_t)iv * VEC);
+            float d[VEC];
+            unpack<T, VEC>(ld_stream<T, VEC>(drr + (int64_t)iv * VEC), d);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) o[i] += Cvt<T>::to_f(d.e[i]);
+            for (int i = 0; i < VEC; ++i) o[i] += d[i];
           }
           Pack<T, VEC> out;
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) out.e[i] = Cvt<T>::from_f(o[i]);
+          pack<T, VEC>(o, out);
           st_stream<T, VEC>(dxr + (int64_t)iv * VEC, out);
         }
       }
@@ -147,7 +137,7 @@ __global__ void __launch_bounds__(BwdMaxThreads<VEC * K>::value) norm_bwd_kernel
     for (int k = 0; k < K; ++k) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        acc_g[k][i] += dyf[k][i] * xh[k][i];
+        acc_g[k][i] = fmaf(dyf[k][i], xh[k][i], acc_g[k][i]);
         if (KIND == FLN_LAYERNORM) acc_b[k][i] += dyf[k][i];
       }
     }
@@ -372,6 +362,32 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
   constexpr int FULL = 16 / sizeof(T);
   const bool want_params = dgamma != nullptr || dbeta != nullptr || dgb_f32 != nullptr;
+  // large aligned problems: persistent bulk-async pipeline for stage 1
+  const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
+  const int64_t pipeP =
+      (aligned && p.dres_in == nullptr) ? bwd_pipeline_partial_rows(KIND, dt, p.rows, p.cols) : 0;
+  if (pipeP > 0) {
+    if (want_params) {
+      const size_t need = (size_t)pipeP * NR * p.cols * sizeof(float);
+      if (workspace == nullptr || workspace_bytes < need || !is_aligned16(workspace))
+        return FLN_ERR_WORKSPACE;
+      p.partials = reinterpret_cast<float*>(workspace);
+    } else {
+      p.partials = nullptr;
+    }
+    const int rc = launch_bwd_pipeline(KIND, dt, p, st);
+    if (rc != FLN_PIPE_NOT_APPLICABLE) {
+      if (rc != FLN_OK) return rc;
+      if (want_params) {
+        const int ncols = NR * p.cols;
+        colreduce_kernel<T><<<(ncols + 31) / 32, 256, 0, st>>>(
+            p.partials, (int)pipeP, ncols, p.cols, dgb_f32, reinterpret_cast<T*>(dgamma),
+            reinterpret_cast<T*>(dbeta));
+        FLN_CHECK_LAUNCH();
+      }
+      return FLN_OK;
+    }
+  }
   BwdLaunch L = plan_bwd<T, KIND>(p.rows, p.cols, aligned);
   if (want_params) {
     const size_t need = (size_t)L.P * NR * p.cols * sizeof(float);
@@ -421,6 +437,9 @@ static size_t ws_bytes_typed(int64_t rows, int cols) {
   if (L1.P > P) P = L1.P;
   if (R.P > P) P = R.P;
   if (R1.P > P) P = R1.P;
+  const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
+  const int64_t pipeP = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols);
+  if (pipeP > P) P = pipeP;
   return (size_t)P * 2 * cols * sizeof(float);
 }
 

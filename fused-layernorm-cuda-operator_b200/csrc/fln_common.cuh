@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "fln_b200.h"
 
 namespace fln {
@@ -100,6 +102,123 @@ __device__ __forceinline__ void st_plain(T* p, const Pack<T, VEC>& v) {
 }
 
 // ------------------------------------------------------------------------------------
+// whole-vector conversions.  The hot loops are issue-bound at bf16, so a 16-bit pair is
+// widened with one shift / one mask and narrowed with one paired round-to-nearest-even
+// convert, instead of element-by-element conversions.
+// ------------------------------------------------------------------------------------
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack(const Pack<T, VEC>& p, float (&f)[VEC]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) f[i] = Cvt<T>::to_f(p.e[i]);
+  } else if constexpr (VEC >= 2) {
+    const unsigned int* w = reinterpret_cast<const unsigned int*>(&p);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        f[2 * j] = __uint_as_float(w[j] << 16);
+        f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      } else {
+        float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        f[2 * j] = t.x;
+        f[2 * j + 1] = t.y;
+      }
+    }
+  } else {
+    f[0] = Cvt<T>::to_f(p.e[0]);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void pack(const float (&f)[VEC], Pack<T, VEC>& p) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p.e[i] = Cvt<T>::from_f(f[i]);
+  } else if constexpr (VEC >= 2) {
+    unsigned int* w = reinterpret_cast<unsigned int*>(&p);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+        w[j] = *reinterpret_cast<unsigned int*>(&t);
+      } else {
+        __half2 t = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+        w[j] = *reinterpret_cast<unsigned int*>(&t);
+      }
+    }
+  } else {
+    p.e[0] = Cvt<T>::from_f(f[0]);
+  }
+}
+
+// Sum over the `tpr` threads that own a row, in two halves around the caller's CTA
+// barrier.  *_warp: butterfly inside the warp (all lanes of the group end up equal) and,
+// for groups of several warps, lane 0 parks the warp's value in shared memory.
+// *_cta: every thread adds the group's per-warp values in the same fixed order, so all of
+// them hold bit-identical totals without further shuffles.
+template <int NV>
+__device__ __forceinline__ void rowsum_warp(float (&v)[NV], int tpr, float* smem) {
+  if (tpr >= 32) {  // the usual case, fully unrolled
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+    }
+  } else {
+    for (int off = tpr >> 1; off > 0; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+    }
+  }
+  if (tpr > 32 && (threadIdx.x & 31) == 0) {
+    const int warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) smem[i * 32 + warp] = v[i];
+  }
+}
+template <int W>
+__device__ __forceinline__ float sum_w(const float* s) {  // s is 16-byte aligned when W >= 4
+  if constexpr (W == 2) {
+    return s[0] + s[1];
+  } else {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; j += 4) {
+      const float4 q = *reinterpret_cast<const float4*>(s + j);
+      t += (q.x + q.y) + (q.z + q.w);
+    }
+    return t;
+  }
+}
+template <int NV>
+__device__ __forceinline__ void rowsum_cta(float (&v)[NV], int tpr, const float* smem) {
+  if (tpr > 32) {
+    const int wpr = tpr >> 5;
+    const int gbase = (threadIdx.x >> 5) & ~(wpr - 1);  // wpr is a power of two
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float* s = smem + i * 32 + gbase;
+      switch (wpr) {
+        case 2:
+          v[i] = sum_w<2>(s);
+          break;
+        case 4:
+          v[i] = sum_w<4>(s);
+          break;
+        case 8:
+          v[i] = sum_w<8>(s);
+          break;
+        case 16:
+          v[i] = sum_w<16>(s);
+          break;
+        default:
+          v[i] = sum_w<32>(s);
+          break;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // activations
 // ------------------------------------------------------------------------------------
 template <int ACT>
@@ -144,6 +263,75 @@ __device__ __forceinline__ Wf wf_shfl_xor(Wf v, int off) {
   o.m2 = __shfl_xor_sync(0xffffffffu, v.m2, off);
   o.n = __shfl_xor_sync(0xffffffffu, v.n, off);
   return o;
+}
+
+// The reductions come in two halves so that a caller can put its own CTA barrier between
+// them: *_pre (warp butterfly, lane 0 of each warp to shared memory), a barrier when
+// tpr > 32, then *_post (combine the per-warp values).
+__device__ __forceinline__ Wf wf_reduce_pre(Wf v, int tpr, float* smem) {
+  const int lane = threadIdx.x & 31;
+  const int lim = tpr < 32 ? tpr : 32;
+  for (int off = lim >> 1; off > 0; off >>= 1) v = wf_merge(v, wf_shfl_xor(v, off));
+  if (tpr > 32 && lane == 0) {
+    const int warp = threadIdx.x >> 5;
+    smem[warp] = v.mean;
+    smem[32 + warp] = v.m2;
+    smem[64 + warp] = v.n;
+  }
+  return v;
+}
+__device__ __forceinline__ Wf wf_reduce_post(Wf v, int tpr, const float* smem) {
+  const int lane = threadIdx.x & 31;
+  if (tpr > 32) {
+    const int warp = threadIdx.x >> 5;
+    const int wpr = tpr >> 5;
+    const int gbase = (warp / wpr) * wpr;
+    Wf w;
+    if (lane < wpr) {
+      w.mean = smem[gbase + lane];
+      w.m2 = smem[32 + gbase + lane];
+      w.n = smem[64 + gbase + lane];
+    } else {
+      w.mean = 0.f;
+      w.m2 = 0.f;
+      w.n = 0.f;
+    }
+    for (int off = wpr >> 1; off > 0; off >>= 1) w = wf_merge(w, wf_shfl_xor(w, off));
+    v = w;
+  }
+  const int src = tpr < 32 ? (lane & ~(tpr - 1)) : 0;
+  v.mean = __shfl_sync(0xffffffffu, v.mean, src);
+  v.m2 = __shfl_sync(0xffffffffu, v.m2, src);
+  return v;
+}
+template <int NV>
+__device__ __forceinline__ void sum_reduce_pre(float (&v)[NV], int tpr, float* smem) {
+  const int lane = threadIdx.x & 31;
+  const int lim = tpr < 32 ? tpr : 32;
+  for (int off = lim >> 1; off > 0; off >>= 1) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+  }
+  if (tpr > 32 && lane == 0) {
+    const int warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) smem[i * 32 + warp] = v[i];
+  }
+}
+template <int NV>
+__device__ __forceinline__ void sum_reduce_post(float (&v)[NV], int tpr, const float* smem) {
+  if (tpr > 32) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int wpr = tpr >> 5;
+    const int gbase = (warp / wpr) * wpr;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = lane < wpr ? smem[i * 32 + gbase + lane] : 0.f;
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+    }
+  }
 }
 
 // smem: 3 * 32 floats per buffer.  Every thread of the CTA must call this.
@@ -202,12 +390,59 @@ __device__ __forceinline__ void group_reduce_sum(float (&v)[NV], int tpr, float*
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NV; ++i) v[i] = lane < wpr ? smem[i * 32 + gbase + lane] : 0.f;
-    for (int off = wpr >> 1; off > 0; off >>= 1) {
+    // lanes >= wpr hold zeros: a full-warp butterfly leaves the total in every lane
+    for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
     }
   }
 }
+
+// ------------------------------------------------------------------------------------
+// kernel parameter blocks (shared by the register-resident and the pipelined kernels)
+// ------------------------------------------------------------------------------------
+struct FwdParams {
+  const void* x;
+  const void* res;
+  const void* gamma;
+  const void* beta;
+  void* y;
+  void* sum_out;
+  float* mean;
+  float* rstd;
+  int64_t rows;
+  int cols;
+  int nv;  // vectors per row
+  int tpr;
+  int log2_tpr;
+  float eps;
+};
+
+struct BwdParams {
+  const void* dy;
+  const void* x;
+  const float* mean;
+  const float* rstd;
+  const void* gamma;
+  const void* dres_in;
+  void* dx;
+  float* partials;  // [P][2][cols] (LayerNorm) or [P][1][cols] (RMSNorm); may be NULL
+  int64_t rows;
+  int64_t row_groups;
+  int cols;
+  int nv;
+  int tpr;
+  int log2_tpr;
+};
+
+// Pipelined (bulk-async staged, persistent) variants, fln_pipeline.cu.  They return
+// FLN_PIPE_NOT_APPLICABLE when the shape is better served by the register kernels.
+constexpr int FLN_PIPE_NOT_APPLICABLE = -1;
+int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p,
+                        cudaStream_t st);
+int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st);
+// partial rows the pipelined backward writes for this shape (0 = not applicable)
+int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols);
 
 // ------------------------------------------------------------------------------------
 // host side: launch plan

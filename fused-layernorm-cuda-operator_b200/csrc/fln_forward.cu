@@ -1,10 +1,13 @@
 // Row-wise LayerNorm / RMSNorm forward for sm_100a.
 //
 // One row is owned by `tpr` consecutive threads; each thread keeps K vectors of the row in
-// registers, so the row is read from HBM exactly once.  Statistics are fp32: per-thread
-// two-pass (mean, M2) over the registers, then a (mean, M2, count) merge across the group
-// by warp shuffles and at most one hop through shared memory.  The epilogue (affine,
-// GELU, down-cast) is applied on the registers and stored with 16-byte vector stores.
+// registers (as floats), so the row is read from HBM exactly once.  Statistics are fp32 and
+// two-pass over the registers: the row is shifted by its first element, summed (warp
+// butterfly + one hop through shared memory) to get the mean, centred, and the squared
+// deviations are summed the same way.  At bf16 this kernel is bound by instruction issue,
+// not by HBM, so the element loop is kept to a handful of instructions: paired widen /
+// narrow conversions, fused multiply-adds, rsqrt.  The epilogue (affine, GELU, down-cast) is
+// applied on the registers and stored with 16-byte vector stores.
 //
 // Stands in for layernorm_kernel / layernorm_gelu_kernel of the reference
 // (csrc/layernorm_cuda_kernel.cu:39-92, 95-148), which read every row three times with
@@ -14,22 +17,6 @@
 
 namespace fln {
 
-struct FwdParams {
-  const void* x;
-  const void* res;
-  const void* gamma;
-  const void* beta;
-  void* y;
-  void* sum_out;
-  float* mean;
-  float* rstd;
-  int64_t rows;
-  int cols;
-  int nv;  // vectors per row
-  int tpr;
-  int log2_tpr;
-  float eps;
-};
 
 template <int K>
 struct MaxThreads {
@@ -38,7 +25,7 @@ struct MaxThreads {
 
 template <typename TI, typename TO, int VEC, int K, int KIND, int ACT>
 __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const FwdParams p) {
-  __shared__ float s_red[96];
+  __shared__ __align__(16) float s_red[2][32];
 
   const int tid = threadIdx.x;
   const int tpr = p.tpr;
@@ -47,19 +34,27 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
   const int rows_per_cta = blockDim.x >> p.log2_tpr;
   const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
   const bool row_ok = row < p.rows;
-  const int64_t base = row * (int64_t)p.cols;
+  const int64_t base = row_ok ? row * (int64_t)p.cols : 0;
+  const float inv_n = 1.0f / (float)p.cols;
 
   const TI* __restrict__ xr = reinterpret_cast<const TI*>(p.x) + base;
 
-  Pack<TI, VEC> raw[K];
+  float c = 0.f;  // shift: element 0 of the row (one extra broadcast load, in flight with the rest)
+  if (KIND == FLN_LAYERNORM) {
+    c = Cvt<TI>::to_f(ld_param<TI, 1>(xr).e[0]);
+    if (p.res != nullptr)
+      c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(ld_param<TI, 1>(reinterpret_cast<const TI*>(p.res) + base).e[0])));
+  }
+  // The whole row goes into registers as floats: HBM is read once.
+  float f[K][VEC];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
     if (row_ok && iv < p.nv) {
-      raw[k] = ld_stream<TI, VEC>(xr + (int64_t)iv * VEC);
+      unpack<TI, VEC>(ld_stream<TI, VEC>(xr + (int64_t)iv * VEC), f[k]);
     } else {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) raw[k].e[i] = Cvt<TI>::from_f(0.f);
+      for (int i = 0; i < VEC; ++i) f[k][i] = 0.f;
     }
   }
   if (p.res != nullptr) {
@@ -71,60 +66,60 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
     for (int k = 0; k < K; ++k) {
       const int iv = lane_r + k * tpr;
       if (row_ok && iv < p.nv) {
-        Pack<TI, VEC> r = ld_stream<TI, VEC>(rr + (int64_t)iv * VEC);
+        float r[VEC];
+        unpack<TI, VEC>(ld_stream<TI, VEC>(rr + (int64_t)iv * VEC), r);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-          raw[k].e[i] = Cvt<TI>::from_f(Cvt<TI>::to_f(raw[k].e[i]) + Cvt<TI>::to_f(r.e[i]));
-        st_stream<TI, VEC>(sr + (int64_t)iv * VEC, raw[k]);
+        for (int i = 0; i < VEC; ++i) f[k][i] += r[i];
+        Pack<TI, VEC> q;
+        pack<TI, VEC>(f[k], q);
+        st_stream<TI, VEC>(sr + (int64_t)iv * VEC, q);
+        unpack<TI, VEC>(q, f[k]);
       }
     }
   }
 
-  // ---- statistics -------------------------------------------------------------------
+  // ---- statistics: shifted two-pass, fp32 ---------------------------------------------
+  // The row is first shifted by its own first element c, so a constant row gives a sum of
+  // exactly zero whatever its magnitude, and |mean| >> std costs no accuracy.
   float mean = 0.f, rstd;
   if (KIND == FLN_LAYERNORM) {
-    float lsum = 0.f, cnt = 0.f;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};  // independent chains: the adds are latency-bound
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      const int iv = lane_r + k * tpr;
-      if (iv < p.nv) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) lsum += Cvt<TI>::to_f(raw[k].e[i]);
-        cnt += (float)VEC;
-      }
-    }
-    Wf w;
-    w.n = cnt;
-    w.mean = cnt > 0.f ? lsum / cnt : 0.f;
-    w.m2 = 0.f;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int iv = lane_r + k * tpr;
-      if (iv < p.nv) {
+      if (lane_r + k * tpr < p.nv) {  // padding vectors stay zero
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          float d = Cvt<TI>::to_f(raw[k].e[i]) - w.mean;
-          w.m2 += d * d;
+          f[k][i] -= c;
+          a4[(k * VEC + i) & 3] += f[k][i];
         }
       }
     }
-    w = group_reduce_wf(w, tpr, s_red);
-    mean = w.mean;
-    float var = w.m2 / (float)p.cols;
-    rstd = 1.0f / sqrtf(var + p.eps);
-  } else {
-    float ss[1] = {0.f};
+    float a[1] = {(a4[0] + a4[1]) + (a4[2] + a4[3])};
+    rowsum_warp<1>(a, tpr, s_red[0]);
+    if (tpr > 32) __syncthreads();
+    rowsum_cta<1>(a, tpr, s_red[0]);
+    const float ms = a[0] * inv_n;  // mean of the shifted row
+    mean = c + ms;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      if (lane_r + k * tpr < p.nv) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float v = Cvt<TI>::to_f(raw[k].e[i]);  // padding vectors are zero
-        ss[0] += v * v;
+        for (int i = 0; i < VEC; ++i) f[k][i] -= ms;
       }
     }
-    group_reduce_sum<1>(ss, tpr, s_red);
-    rstd = 1.0f / sqrtf(ss[0] / (float)p.cols + p.eps);
   }
+  float q4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) q4[(k * VEC + i) & 3] = fmaf(f[k][i], f[k][i], q4[(k * VEC + i) & 3]);
+  }
+  float q[1] = {(q4[0] + q4[1]) + (q4[2] + q4[3])};
+  rowsum_warp<1>(q, tpr, s_red[1]);
+  if (tpr > 32) __syncthreads();
+  rowsum_cta<1>(q, tpr, s_red[1]);
+  rstd = rsqrtf(q[0] * inv_n + p.eps);
+
   if (row_ok && lane_r == 0) {
     if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
     if (p.rstd != nullptr) p.rstd[row] = rstd;
@@ -138,23 +133,26 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
     if (row_ok && iv < p.nv) {
-      float v[VEC];
+      float o[VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
+      for (int i = 0; i < VEC; ++i) o[i] = f[k][i] * rstd;
       if (gp != nullptr) {
-        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
+        float g[VEC];
+        unpack<TI, VEC>(ld_param<TI, VEC>(gp + (int64_t)iv * VEC), g);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
+        for (int i = 0; i < VEC; ++i) o[i] *= g[i];
       }
       if (bp != nullptr) {
-        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
+        float b[VEC];
+        unpack<TI, VEC>(ld_param<TI, VEC>(bp + (int64_t)iv * VEC), b);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
+        for (int i = 0; i < VEC; ++i) o[i] += b[i];
       }
-      Pack<TO, VEC> o;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) o.e[i] = Cvt<TO>::from_f(apply_act<ACT>(v[i]));
-      st_stream<TO, VEC>(yr + (int64_t)iv * VEC, o);
+      for (int i = 0; i < VEC; ++i) o[i] = apply_act<ACT>(o[i]);
+      Pack<TO, VEC> out;
+      pack<TO, VEC>(o, out);
+      st_stream<TO, VEC>(yr + (int64_t)iv * VEC, out);
     }
   }
 }
@@ -316,6 +314,12 @@ extern "C" int fln_norm_forward(int kind, const void* x, const void* residual, c
   const bool aligned = is_aligned16(x) && is_aligned16(y) && is_aligned16(residual) &&
                        is_aligned16(sum_out) && is_aligned16(gamma) && is_aligned16(beta);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == FLN_RMSNORM && act != FLN_ACT_NONE) return FLN_ERR_UNSUPPORTED;
+  if (aligned) {
+    // large aligned problems: persistent bulk-async pipeline
+    const int rc = launch_fwd_pipeline(kind, act, io_dtype, out_dtype, p, st);
+    if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+  }
   if (io_dtype == FLN_F32 && out_dtype == FLN_F32)
     return launch_kind_act<float, float>(kind, act, p, aligned, st);
   if (io_dtype == FLN_F32 && out_dtype == FLN_BF16)

@@ -1,0 +1,709 @@
+// Persistent, bulk-async staged LayerNorm / RMSNorm forward and backward for sm_100a.
+//
+// Every CTA is persistent and owns a ring of S shared-memory stages; one elected thread
+// keeps the ring full with 1-D bulk copies (cp.async.bulk global -> shared, completion
+// signalled on an mbarrier with complete_tx::bytes), so up to S tiles per CTA are in flight
+// regardless of register use.  A tile is R consecutive rows, which are contiguous in
+// memory, so one tile is ONE bulk copy per input tensor.  Consumers wait on the stage's
+// mbarrier, pull their vectors from shared memory into registers, and the first CTA barrier
+// of the row reduction doubles as the "stage is free again" signal after which the producer
+// refills it.  gamma / beta live in registers as floats for the life of the CTA, so the only
+// L2 traffic per row is the row itself.
+//
+// At bf16 these kernels are bound by instruction issue before they are bound by HBM, so the
+// per-element instruction count is what matters.  The FULL instantiation (row length equal
+// to K * threads-per-row, no ragged last tile, at least a warp per row) has no predication
+// at all in the loop; the general instantiation keeps the bounds checks.
+//
+// No cluster multicast is used anywhere; every copy is CTA-local.
+//
+// Every mbarrier wait is bounded: on a time-out the CTA votes, raises the device status word
+// (fln_device_status), lets its producer wait -- again bounded -- for copies still in flight,
+// and returns.
+#include <string.h>
+
+#include <atomic>
+
+#include "fln_common.cuh"
+
+namespace fln {
+
+__device__ int g_device_status = 0;
+
+struct PipeGeom {
+  int R;         // rows per tile
+  int tpr;       // threads per row
+  int log2_tpr;
+  int S;         // stages
+  uint32_t row_bytes;
+  uint32_t second_off;    // byte offset of the second tensor inside a stage
+  uint32_t stage_stride;  // bytes per stage
+};
+
+constexpr int kSmemHeader = 2048;  // mbarriers + reduction scratch in front of the stages
+constexpr uint32_t kWaitLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// global -> this CTA's shared memory, 16-byte aligned on both sides, bytes % 16 == 0
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kWaitLimit; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// tiles of CTA b: t = b + i * gridDim.x  (evaluated once per CTA)
+__device__ __forceinline__ int my_tile_count(int64_t n_tiles) {
+  return (int64_t)blockIdx.x < n_tiles ? (int)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+}
+
+// After a failed vote: thread 0 raises the status word and gives copies already issued a
+// bounded chance to land before the CTA's shared memory is released.
+__device__ __forceinline__ void pipeline_abort(uint64_t* full, int S, int s, uint32_t phase, int outstanding) {
+  if (threadIdx.x == 0) {
+    atomicExch(&g_device_status, 1);
+    for (int j = 0; j < outstanding; ++j) {
+      mbar_wait_bounded(&full[s], phase);
+      if (++s == S) {
+        s = 0;
+        phase ^= 1u;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// forward
+//
+// Per element: one shift or mask (widen), shift by c and add (row sum), centre, one fma
+// (sum of squares), one multiply and one fma (normalize + affine), half a paired convert.
+// Statistics are the two-pass form on the row shifted by its first element, each pass
+// reduced by a warp butterfly plus one shared-memory hop.
+// ----------------------------------------------------------------------------------------
+template <typename TI, typename TO, int K, int KIND, int ACT, bool FULL>
+__global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
+  constexpr int VEC = 16 / sizeof(TI);
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  float* s_red = reinterpret_cast<float*>(smem + 256);  // 4 x 32 floats
+  unsigned char* stages = smem + kSmemHeader;
+
+  const int tid = threadIdx.x;
+  const int tpr = g.tpr;
+  const int lane_r = tid & (tpr - 1);
+  const int r_in = tid >> g.log2_tpr;
+  const int S = g.S;
+  const int my_tiles = my_tile_count((p.rows + g.R - 1) / g.R);
+  const bool has_res = p.res != nullptr;
+  const float inv_n = 1.0f / (float)p.cols;
+  const float eps = p.eps;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  // tile i of this CTA into stage s (the caller tracks s; no division in the loop)
+  auto issue = [&](int i, int s) {
+    const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)i * gridDim.x) * g.R;
+    const int64_t left = p.rows - row0;
+    const uint32_t bytes = (uint32_t)(left < g.R ? left : g.R) * g.row_bytes;
+    unsigned char* dst = stages + (size_t)s * g.stage_stride;
+    mbar_expect_tx(&full[s], has_res ? 2 * bytes : bytes);
+    bulk_g2s(dst, reinterpret_cast<const TI*>(p.x) + row0 * p.cols, bytes, &full[s]);
+    if (has_res) bulk_g2s(dst + g.second_off, reinterpret_cast<const TI*>(p.res) + row0 * p.cols, bytes, &full[s]);
+  };
+  if (tid == 0) {
+    const int pre = my_tiles < S ? my_tiles : S;
+    for (int i = 0; i < pre; ++i) issue(i, i);
+  }
+
+  float gam[K][VEC], bet[K][VEC];
+  bool vok[K];  // does vector k of this thread exist in the row
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    vok[k] = FULL ? true : iv < p.nv;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      gam[k][e] = 1.f;
+      bet[k][e] = 0.f;
+    }
+    if (vok[k]) {
+      if (p.gamma != nullptr)
+        unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
+      if (p.beta != nullptr)
+        unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC), bet[k]);
+    }
+  }
+
+  int s = 0;
+  uint32_t phase = 0;
+  int64_t row = (int64_t)blockIdx.x * g.R + r_in;
+  const int64_t row_step = (int64_t)gridDim.x * g.R;
+  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * 16u;
+  const uint32_t k_off = (uint32_t)tpr * 16u;
+  for (int i = 0; i < my_tiles; ++i, row += row_step) {
+    const bool landed = mbar_wait_bounded(&full[s], phase);
+    const bool row_ok = FULL ? true : row < p.rows;
+    const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
+    float* redA = s_red + (i & 1) * 32;
+    float* redB = s_red + 64 + (i & 1) * 32;
+
+    float f[K][VEC];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (FULL || (row_ok && vok[k])) {
+        unpack<TI, VEC>(*reinterpret_cast<const Pack<TI, VEC>*>(st + k * k_off), f[k]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) f[k][e] = 0.f;
+      }
+    }
+    if (has_res) {
+      TI* __restrict__ sr = reinterpret_cast<TI*>(p.sum_out) + row * (int64_t)p.cols + (int64_t)lane_r * VEC;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        if (FULL || (row_ok && vok[k])) {
+          float r[VEC];
+          unpack<TI, VEC>(*reinterpret_cast<const Pack<TI, VEC>*>(st + g.second_off + k * k_off), r);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) f[k][e] += r[e];
+          // the sum is rounded to the I/O type first: that value is normalized and stored
+          Pack<TI, VEC> q;
+          pack<TI, VEC>(f[k], q);
+          st_stream<TI, VEC>(sr + (int64_t)k * tpr * VEC, q);
+          unpack<TI, VEC>(q, f[k]);
+        }
+      }
+    }
+
+    float mean = 0.f;
+    if (KIND == FLN_LAYERNORM) {
+      // shift by element 0 of the row (a broadcast read of the stage): a constant row then
+      // sums to exactly zero whatever its magnitude, and |mean| >> std costs no accuracy
+      const unsigned char* st0 = st - (size_t)lane_r * 16;
+      float c = Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0));
+      if (has_res)
+        c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0 + g.second_off))));
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four chains: the adds are latency-bound
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        if (FULL || vok[k]) {  // padding vectors stay zero
+#pragma unroll
+          for (int e = 0; e < VEC; e += 4) {
+            f[k][e] -= c;
+            f[k][e + 1] -= c;
+            f[k][e + 2] -= c;
+            f[k][e + 3] -= c;
+            a0 += f[k][e];
+            a1 += f[k][e + 1];
+            a2 += f[k][e + 2];
+            a3 += f[k][e + 3];
+          }
+        }
+      }
+      float a[1] = {(a0 + a1) + (a2 + a3)};
+      rowsum_warp<1>(a, tpr, redA);
+      // The first barrier of a tile also proves that every thread has pulled its part of
+      // stage s into registers, so the producer may refill the stage right after it.
+      if (!__syncthreads_and(landed ? 1 : 0)) {
+        pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
+        return;
+      }
+      if (tid == 0 && i + S < my_tiles) issue(i + S, s);
+      rowsum_cta<1>(a, tpr, redA);
+      const float ms = a[0] * inv_n;  // mean of the shifted row
+      mean = c + ms;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        if (FULL || vok[k]) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) f[k][e] -= ms;
+        }
+      }
+    }
+    float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        q0 = fmaf(f[k][e], f[k][e], q0);
+        q1 = fmaf(f[k][e + 1], f[k][e + 1], q1);
+        q2 = fmaf(f[k][e + 2], f[k][e + 2], q2);
+        q3 = fmaf(f[k][e + 3], f[k][e + 3], q3);
+      }
+    }
+    float q[1] = {(q0 + q1) + (q2 + q3)};
+    rowsum_warp<1>(q, tpr, redB);
+    if (KIND == FLN_LAYERNORM) {
+      __syncthreads();
+    } else {
+      if (!__syncthreads_and(landed ? 1 : 0)) {
+        pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
+        return;
+      }
+      if (tid == 0 && i + S < my_tiles) issue(i + S, s);
+    }
+    rowsum_cta<1>(q, tpr, redB);
+    const float rstd = rsqrtf(fmaf(q[0], inv_n, eps));
+
+    if (row_ok && lane_r == 0) {
+      if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
+      if (p.rstd != nullptr) p.rstd[row] = rstd;
+    }
+    TO* __restrict__ yr = reinterpret_cast<TO*>(p.y) + row * (int64_t)p.cols + (int64_t)lane_r * VEC;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (FULL || (row_ok && vok[k])) {
+        float o[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = apply_act<ACT>(fmaf(f[k][e] * rstd, gam[k][e], bet[k][e]));
+        Pack<TO, VEC> out;
+        pack<TO, VEC>(o, out);
+        st_stream<TO, VEC>(yr + (int64_t)k * tpr * VEC, out);
+      }
+    }
+    if (++s == S) {
+      s = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// backward (stage 1: dx and per-CTA partial sums of dgamma / dbeta)
+//
+// Per element: two widening shifts, (x - mean) * rstd, g = dy * gamma, two running sums,
+// then dx = rstd * ((g - c2) - xhat * c1) and the two column accumulators.
+// ----------------------------------------------------------------------------------------
+template <typename T, int K, int KIND, bool FULL>
+__global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, const PipeGeom g) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 floats
+  unsigned char* stages = smem + kSmemHeader;
+
+  const int tid = threadIdx.x;
+  const int tpr = g.tpr;
+  const int lane_r = tid & (tpr - 1);
+  const int r_in = tid >> g.log2_tpr;
+  const int S = g.S;
+  const int my_tiles = my_tile_count((p.rows + g.R - 1) / g.R);
+  const float inv_n = 1.0f / (float)p.cols;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  auto issue = [&](int i, int s) {
+    const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)i * gridDim.x) * g.R;
+    const int64_t left = p.rows - row0;
+    const uint32_t bytes = (uint32_t)(left < g.R ? left : g.R) * g.row_bytes;
+    unsigned char* dst = stages + (size_t)s * g.stage_stride;
+    mbar_expect_tx(&full[s], 2 * bytes);
+    bulk_g2s(dst, reinterpret_cast<const T*>(p.dy) + row0 * p.cols, bytes, &full[s]);
+    bulk_g2s(dst + g.second_off, reinterpret_cast<const T*>(p.x) + row0 * p.cols, bytes, &full[s]);
+  };
+  if (tid == 0) {
+    const int pre = my_tiles < S ? my_tiles : S;
+    for (int i = 0; i < pre; ++i) issue(i, i);
+  }
+
+  float acc_g[K][VEC], acc_b[K][VEC], gam[K][VEC];
+  bool vok[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int iv = lane_r + k * tpr;
+    vok[k] = FULL ? true : iv < p.nv;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      acc_g[k][e] = 0.f;
+      acc_b[k][e] = 0.f;
+      gam[k][e] = 1.f;
+    }
+    if (p.gamma != nullptr && vok[k])
+      unpack<T, VEC>(ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
+  }
+
+  // per-row statistics of the next tile are fetched one iteration ahead
+  int64_t row = (int64_t)blockIdx.x * g.R + r_in;
+  const int64_t row_step = (int64_t)gridDim.x * g.R;
+  float mean_n = 0.f, rstd_n = 0.f;
+  if (my_tiles > 0 && row < p.rows) {
+    if (KIND == FLN_LAYERNORM) mean_n = __ldg(p.mean + row);
+    rstd_n = __ldg(p.rstd + row);
+  }
+
+  int s = 0;
+  uint32_t phase = 0;
+  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * 16u;
+  const uint32_t k_off = (uint32_t)tpr * 16u;
+  for (int i = 0; i < my_tiles; ++i, row += row_step) {
+    const bool row_ok = FULL ? true : row < p.rows;
+    const float mean = mean_n, rstd = rstd_n;
+    if (i + 1 < my_tiles) {
+      const int64_t rown = row + row_step;
+      mean_n = 0.f;
+      rstd_n = 0.f;
+      if (rown < p.rows) {
+        if (KIND == FLN_LAYERNORM) mean_n = __ldg(p.mean + rown);
+        rstd_n = __ldg(p.rstd + rown);
+      }
+    }
+    const bool landed = mbar_wait_bounded(&full[s], phase);
+    const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
+
+    float xh[K][VEC], dyf[K][VEC];
+    float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (FULL || (row_ok && vok[k])) {
+        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + k * k_off), dyf[k]);
+        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + g.second_off + k * k_off), xh[k]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) xh[k][e] = (xh[k][e] - mean) * rstd;
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          dyf[k][e] = 0.f;
+          xh[k][e] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; e += 2) {
+        const float g0 = dyf[k][e] * gam[k][e], g1 = dyf[k][e + 1] * gam[k][e + 1];
+        r0a = fmaf(g0, xh[k][e], r0a);
+        r0b = fmaf(g1, xh[k][e + 1], r0b);
+        if (KIND == FLN_LAYERNORM) {
+          r1a += g0;
+          r1b += g1;
+        }
+      }
+    }
+    float red[NR];
+    red[0] = r0a + r0b;
+    if (KIND == FLN_LAYERNORM) red[NR - 1] = r1a + r1b;
+    float* sr = s_red + (i & 1) * 64;
+    rowsum_warp<NR>(red, tpr, sr);
+    if (!__syncthreads_and(landed ? 1 : 0)) {
+      pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
+      return;
+    }
+    if (tid == 0 && i + S < my_tiles) issue(i + S, s);
+    rowsum_cta<NR>(red, tpr, sr);
+    // dx = rstd * ((g - c2) - xhat * c1): the subtraction comes first so that rows whose g
+    // is (nearly) constant cancel exactly instead of leaving a rounding residue times rstd
+    const float nc1 = -(red[0] * inv_n);
+    const float c2 = KIND == FLN_LAYERNORM ? red[NR - 1] * inv_n : 0.f;
+
+    if (p.dx != nullptr) {
+      T* __restrict__ dxr = reinterpret_cast<T*>(p.dx) + row * (int64_t)p.cols + (int64_t)lane_r * VEC;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        if (FULL || (row_ok && vok[k])) {
+          float o[VEC];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[e] = rstd * fmaf(xh[k][e], nc1, dyf[k][e] * gam[k][e] - c2);
+          Pack<T, VEC> out;
+          pack<T, VEC>(o, out);
+          st_stream<T, VEC>(dxr + (int64_t)k * tpr * VEC, out);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        acc_g[k][e] = fmaf(dyf[k][e], xh[k][e], acc_g[k][e]);
+        if (KIND == FLN_LAYERNORM) acc_b[k][e] += dyf[k][e];
+      }
+    }
+    if (++s == S) {
+      s = 0;
+      phase ^= 1u;
+    }
+  }
+
+  if (p.partials != nullptr) {
+    const int64_t prow = (int64_t)blockIdx.x * g.R + r_in;
+    float* __restrict__ pg = p.partials + prow * (int64_t)(NR * p.cols);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (vok[k]) {
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4) {
+          *reinterpret_cast<float4*>(pg + (int64_t)iv * VEC + e) =
+              make_float4(acc_g[k][e], acc_g[k][e + 1], acc_g[k][e + 2], acc_g[k][e + 3]);
+          if (KIND == FLN_LAYERNORM)
+            *reinterpret_cast<float4*>(pg + p.cols + (int64_t)iv * VEC + e) =
+                make_float4(acc_b[k][e], acc_b[k][e + 1], acc_b[k][e + 2], acc_b[k][e + 3]);
+        }
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// host: geometry and dispatch
+// ----------------------------------------------------------------------------------------
+static std::atomic<int> g_path_override{0};  // 0 auto, 1 register kernels only, 2 pipeline whenever it fits
+
+struct PipePlan {
+  bool ok;
+  bool full;  // branch-free instantiation applies
+  int K;
+  int threads;
+  int grid;
+  size_t smem;
+  PipeGeom g;
+};
+
+static int ilog2i(int v) {
+  int l = 0;
+  while ((1 << l) < v) ++l;
+  return l;
+}
+static int next_pow2i(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// tensors: how many input tensors are staged per tile (1 or 2)
+static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors) {
+  PipePlan P;
+  memset(&P, 0, sizeof(P));
+  const int vec = 16 / elem_bytes;
+  if (cols % vec != 0 || rows <= 0) return P;
+  const int nv = cols / vec;
+  const int cta_threads = backward ? 512 : 256;
+  // vectors per thread: forward 64 B per thread, backward about 16 columns per thread
+  const int pref = backward ? (16 / vec) : 4;
+  // register budget at 512 threads (128 registers): backward at most 16 columns per
+  // thread, forward at most 32 elements per thread
+  const int maxK = backward ? 16 / vec : 32 / vec;
+  int K = 0, tpr = 0;
+  int fK = 0, ftpr = 0;
+  plan_override(&fK, &ftpr);
+  if (fK > 0 && ftpr >= 8 && ftpr <= 512 && (ftpr & (ftpr - 1)) == 0 && fK <= maxK &&
+      (fK & (fK - 1)) == 0 && (int64_t)fK * ftpr >= nv) {
+    K = fK;
+    tpr = ftpr;
+  }
+  for (int k = pref; k <= maxK && K == 0; k <<= 1) {
+    int t = next_pow2i((nv + k - 1) / k);
+    if (t > 512) continue;
+    if (t < 8) t = 8;
+    int kk = next_pow2i((nv + t - 1) / t);
+    K = kk;
+    tpr = t;
+  }
+  if (K == 0) return P;
+  const int threads = tpr > cta_threads ? tpr : cta_threads;
+  const int R = threads / tpr;
+  const uint32_t row_bytes = (uint32_t)cols * elem_bytes;
+  const uint32_t tile_bytes = row_bytes * R;
+  const uint32_t stage = tile_bytes * tensors;
+  // forward: two CTAs per SM with ~100 KB each; backward: one 512-thread CTA with ~200 KB
+  const size_t budget = backward ? 200 * 1024 : 100 * 1024;
+  int S = (int)((budget - kSmemHeader) / stage);
+  if (S > 16) S = 16;
+  if (S < 2) {
+    // try the whole SM for one CTA
+    S = (int)((220 * 1024 - kSmemHeader) / stage);
+    if (S > 16) S = 16;
+    if (S < 2) return P;
+  }
+  P.ok = true;
+  P.full = tpr >= 32 && (int64_t)K * tpr == nv && rows % R == 0;
+  P.K = K;
+  P.threads = threads;
+  P.smem = kSmemHeader + (size_t)S * stage;
+  P.g.R = R;
+  P.g.tpr = tpr;
+  P.g.log2_tpr = ilog2i(tpr);
+  P.g.S = S;
+  P.g.row_bytes = row_bytes;
+  P.g.second_off = tile_bytes;
+  P.g.stage_stride = stage;
+  const int64_t n_tiles = (rows + R - 1) / R;
+  const int by_smem = (int)((227 * 1024) / P.smem), by_threads = 2048 / threads;
+  const int per_sm = by_smem < by_threads ? by_smem : by_threads;
+  const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
+  P.grid = (int)(n_tiles < cap ? n_tiles : cap);
+  return P;
+}
+
+static bool pipeline_wanted(const PipePlan& P, int64_t rows) {
+  const int ov = g_path_override.load(std::memory_order_relaxed);
+  if (!P.ok || ov == 1) return false;
+  if (ov == 2) return true;
+  // worth it once every CTA streams several tiles
+  const int64_t n_tiles = (rows + P.g.R - 1) / P.g.R;
+  return n_tiles >= 4LL * P.grid || n_tiles >= 8LL * sm_count();
+}
+
+template <typename F>
+static int set_smem(F kernel, size_t smem) {
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return FLN_ERR_LAUNCH;
+    }
+  }
+  return FLN_OK;
+}
+
+template <typename TI, typename TO, int KIND, int ACT>
+static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+#define FLN_LAUNCH(KK, FF)                                                                   \
+  {                                                                                          \
+    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, FF>;                             \
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                             \
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                         \
+  }
+#define FLN_CASE(KK)                  \
+  case KK:                            \
+    if (P.full) FLN_LAUNCH(KK, true)  \
+    else FLN_LAUNCH(KK, false)        \
+    break;
+  switch (P.K) {
+    FLN_CASE(1) FLN_CASE(2) FLN_CASE(4) FLN_CASE(8)
+    default:
+      return FLN_PIPE_NOT_APPLICABLE;
+  }
+#undef FLN_CASE
+#undef FLN_LAUNCH
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
+}
+
+template <typename TI, typename TO>
+static int fwd_pipe_typed(int kind, int act, const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (kind == FLN_RMSNORM) return fwd_pipe_k<TI, TO, FLN_RMSNORM, FLN_ACT_NONE>(p, P, st);
+  switch (act) {
+    case FLN_ACT_NONE:
+      return fwd_pipe_k<TI, TO, FLN_LAYERNORM, FLN_ACT_NONE>(p, P, st);
+    case FLN_ACT_GELU_TANH:
+      return fwd_pipe_k<TI, TO, FLN_LAYERNORM, FLN_ACT_GELU_TANH>(p, P, st);
+    case FLN_ACT_GELU_ERF:
+      return fwd_pipe_k<TI, TO, FLN_LAYERNORM, FLN_ACT_GELU_ERF>(p, P, st);
+  }
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
+int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p0,
+                        cudaStream_t st) {
+  const int es = io_dtype == FLN_F32 ? 4 : 2;
+  PipePlan P = plan_pipeline(false, p0.rows, p0.cols, es, p0.res != nullptr ? 2 : 1);
+  if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
+  FwdParams p = p0;
+  p.nv = p.cols / (16 / es);
+  if (io_dtype == FLN_F32 && out_dtype == FLN_F32) return fwd_pipe_typed<float, float>(kind, act, p, P, st);
+  if (io_dtype == FLN_F32 && out_dtype == FLN_BF16) return fwd_pipe_typed<float, __nv_bfloat16>(kind, act, p, P, st);
+  if (io_dtype == FLN_BF16) return fwd_pipe_typed<__nv_bfloat16, __nv_bfloat16>(kind, act, p, P, st);
+  return fwd_pipe_typed<__half, __half>(kind, act, p, P, st);
+}
+
+template <typename T, int KIND>
+static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+#define FLN_LAUNCH(KK, FF)                                                                   \
+  {                                                                                          \
+    auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF>;                \
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                             \
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                         \
+  }
+#define FLN_CASE(KK)                                       \
+  case KK:                                                 \
+    if (VEC * KK > 16) return FLN_PIPE_NOT_APPLICABLE;     \
+    if (P.full) FLN_LAUNCH(KK, true)                       \
+    else FLN_LAUNCH(KK, false)                             \
+    break;
+  switch (P.K) {
+    FLN_CASE(1) FLN_CASE(2) FLN_CASE(4)
+    default:
+      return FLN_PIPE_NOT_APPLICABLE;
+  }
+#undef FLN_CASE
+#undef FLN_LAUNCH
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
+}
+
+int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols) {
+  (void)kind;
+  const int es = dtype == FLN_F32 ? 4 : 2;
+  PipePlan P = plan_pipeline(true, rows, cols, es, 2);
+  if (!pipeline_wanted(P, rows)) return 0;
+  return (int64_t)P.grid * P.g.R;
+}
+
+int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t st) {
+  const int es = dtype == FLN_F32 ? 4 : 2;
+  PipePlan P = plan_pipeline(true, p0.rows, p0.cols, es, 2);
+  if (!pipeline_wanted(P, p0.rows) || p0.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
+  BwdParams p = p0;
+  p.nv = p.cols / (16 / es);
+#define FLN_RUN(T) \
+  (kind == FLN_LAYERNORM ? bwd_pipe_k<T, FLN_LAYERNORM>(p, P, st) : bwd_pipe_k<T, FLN_RMSNORM>(p, P, st))
+  if (dtype == FLN_F32) return FLN_RUN(float);
+  if (dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
+  return FLN_RUN(__half);
+#undef FLN_RUN
+}
+
+}  // namespace fln
+
+using namespace fln;
+
+extern "C" void fln_set_path_override(int mode) { g_path_override.store(mode, std::memory_order_relaxed); }
+
+extern "C" int fln_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  }
+  return v;
+}

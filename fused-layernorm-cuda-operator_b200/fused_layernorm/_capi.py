@@ -28,6 +28,7 @@ SYMBOLS = [
     "fln_backward_workspace_bytes", "fln_layernorm_backward", "fln_norm_backward", "fln_cast_from_f32",
     "fln_graph_begin", "fln_graph_stream", "fln_graph_end", "fln_graph_launch", "fln_graph_destroy",
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
+    "fln_set_path_override", "fln_device_status",
 ]
 
 
@@ -76,6 +77,9 @@ def lib() -> C.CDLL:
     L.fln_describe_launch.argtypes = [i32, i64, i64, i32, i32, C.POINTER(LaunchInfo)]
     L.fln_set_plan_override.argtypes = [i32, i32]
     L.fln_set_plan_override.restype = None
+    L.fln_set_path_override.argtypes = [i32]
+    L.fln_set_path_override.restype = None
+    L.fln_device_status.restype = i32
     _lib = L
     return L
 

@@ -199,6 +199,18 @@ int fln_describe_launch(int backward, int64_t rows, int64_t cols, int dtype, int
  * Combinations that cannot hold a row fall back to automatic selection. */
 void fln_set_plan_override(int vecs_per_thread, int threads_per_row);
 
+/* Tuning hook: which kernel family serves aligned problems.  0 = automatic (the persistent
+ * bulk-async pipeline once every CTA streams several tiles, register-resident kernels
+ * otherwise), 1 = register-resident kernels only, 2 = the pipeline whenever the row fits.
+ * Query fln_backward_workspace_bytes again after changing it. */
+void fln_set_path_override(int mode);
+
+/* Reads and clears the device status word of the current device (synchronizes the device).
+ * 0 = no kernel reported a problem; 1 = a pipelined kernel gave up waiting for a bulk copy
+ * (its outputs are then incomplete); -1 = the status could not be read.  The reference has
+ * no error reporting on its launch path (csrc/layernorm_cuda_kernel.cu:171,199). */
+int fln_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif
