@@ -23,9 +23,16 @@ struct MaxThreads {
   static constexpr int value = K <= 2 ? 1024 : 512;
 };
 
-template <typename TI, typename TO, int VEC, int K, int KIND, int ACT>
+// FULL: the row is exactly K * tpr vectors long, every CTA holds only valid rows and a row
+// spans at least a warp, so the body carries no bounds checks at all.
+// MODE 0: general; 1: FULL; 2: FULL and the CTA owns exactly one row (one-barrier LayerNorm
+// statistics, see below; measured slower on B200 -- register pressure -- so the launcher
+// does not select it).
+template <typename TI, typename TO, int VEC, int K, int KIND, int ACT, int MODE>
 __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const FwdParams p) {
-  __shared__ __align__(16) float s_red[2][32];
+  constexpr bool FULL = MODE >= 1;
+  constexpr bool ONE = MODE == 2 && KIND == FLN_LAYERNORM;
+  __shared__ __align__(16) float s_red[3][32];
 
   const int tid = threadIdx.x;
   const int tpr = p.tpr;
@@ -33,7 +40,7 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
   const int row_in_cta = tid >> p.log2_tpr;
   const int rows_per_cta = blockDim.x >> p.log2_tpr;
   const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
-  const bool row_ok = row < p.rows;
+  const bool row_ok = FULL ? true : row < p.rows;
   const int64_t base = row_ok ? row * (int64_t)p.cols : 0;
   const float inv_n = 1.0f / (float)p.cols;
 
@@ -50,7 +57,7 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (row_ok && iv < p.nv) {
+    if (FULL || (row_ok && iv < p.nv)) {
       unpack<TI, VEC>(ld_stream<TI, VEC>(xr + (int64_t)iv * VEC), f[k]);
     } else {
 #pragma unroll
@@ -65,7 +72,7 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int iv = lane_r + k * tpr;
-      if (row_ok && iv < p.nv) {
+      if (FULL || (row_ok && iv < p.nv)) {
         float r[VEC];
         unpack<TI, VEC>(ld_stream<TI, VEC>(rr + (int64_t)iv * VEC), r);
 #pragma unroll
@@ -78,47 +85,67 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
     }
   }
 
-  // ---- statistics: shifted two-pass, fp32 ---------------------------------------------
-  // The row is first shifted by its own first element c, so a constant row gives a sum of
-  // exactly zero whatever its magnitude, and |mean| >> std costs no accuracy.
-  float mean = 0.f, rstd;
+  // ---- statistics: fp32, on the row shifted by its first element c ----------------------
+  // The shift makes a constant row sum to exactly zero whatever its magnitude, and keeps
+  // |mean| >> std from costing accuracy.  General form: two passes (sum, then centred sum of
+  // squares), one reduction each.  ONE (the CTA owns exactly one row): both sums in one
+  // reduction, variance = E[d^2] - E[d]^2; its relative error grows like eps (1 + 2 ms^2 /
+  // var), so it is trusted only when the shift element lay within two standard deviations
+  // of the mean, else the exact centred pass runs.  ms and var1 are bit-identical in every
+  // thread of the CTA, so that branch and its barrier are uniform.
+  float mean = 0.f, rstd = 0.f;
+  bool need_second = true;
   if (KIND == FLN_LAYERNORM) {
     float a4[4] = {0.f, 0.f, 0.f, 0.f};  // independent chains: the adds are latency-bound
+    float b4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      if (lane_r + k * tpr < p.nv) {  // padding vectors stay zero
+      if (FULL || lane_r + k * tpr < p.nv) {  // padding vectors stay zero
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           f[k][i] -= c;
           a4[(k * VEC + i) & 3] += f[k][i];
+          if (ONE) b4[(k * VEC + i) & 3] = fmaf(f[k][i], f[k][i], b4[(k * VEC + i) & 3]);
         }
       }
     }
-    float a[1] = {(a4[0] + a4[1]) + (a4[2] + a4[3])};
-    rowsum_warp<1>(a, tpr, s_red[0]);
+    constexpr int NA = ONE ? 2 : 1;
+    float a[NA];
+    a[0] = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+    if (ONE) a[NA - 1] = (b4[0] + b4[1]) + (b4[2] + b4[3]);
+    rowsum_warp<NA>(a, tpr, s_red[0]);
     if (tpr > 32) __syncthreads();
-    rowsum_cta<1>(a, tpr, s_red[0]);
+    rowsum_cta<NA>(a, tpr, s_red[0]);
     const float ms = a[0] * inv_n;  // mean of the shifted row
     mean = c + ms;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      if (lane_r + k * tpr < p.nv) {
+      if (FULL || lane_r + k * tpr < p.nv) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) f[k][i] -= ms;
       }
     }
+    if (ONE) {
+      const float var1 = fmaf(a[NA - 1], inv_n, -ms * ms);
+      if (ms * ms <= 4.f * var1) {
+        need_second = false;
+        rstd = rsqrtf(var1 + p.eps);
+      }
+    }
   }
-  float q4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (need_second) {
+    float q4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
+    for (int k = 0; k < K; ++k) {
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) q4[(k * VEC + i) & 3] = fmaf(f[k][i], f[k][i], q4[(k * VEC + i) & 3]);
+      for (int i = 0; i < VEC; ++i) q4[(k * VEC + i) & 3] = fmaf(f[k][i], f[k][i], q4[(k * VEC + i) & 3]);
+    }
+    float q[1] = {(q4[0] + q4[1]) + (q4[2] + q4[3])};
+    rowsum_warp<1>(q, tpr, s_red[2]);
+    if (tpr > 32) __syncthreads();
+    rowsum_cta<1>(q, tpr, s_red[2]);
+    rstd = rsqrtf(q[0] * inv_n + p.eps);
   }
-  float q[1] = {(q4[0] + q4[1]) + (q4[2] + q4[3])};
-  rowsum_warp<1>(q, tpr, s_red[1]);
-  if (tpr > 32) __syncthreads();
-  rowsum_cta<1>(q, tpr, s_red[1]);
-  rstd = rsqrtf(q[0] * inv_n + p.eps);
 
   if (row_ok && lane_r == 0) {
     if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
@@ -132,17 +159,22 @@ __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const Fw
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (row_ok && iv < p.nv) {
+    if (FULL || (row_ok && iv < p.nv)) {
       float o[VEC];
 #pragma unroll
       for (int i = 0; i < VEC; ++i) o[i] = f[k][i] * rstd;
-      if (gp != nullptr) {
+      if (gp != nullptr && bp != nullptr) {  // the usual case: one fma per element
+        float g[VEC], b[VEC];
+        unpack<TI, VEC>(ld_param<TI, VEC>(gp + (int64_t)iv * VEC), g);
+        unpack<TI, VEC>(ld_param<TI, VEC>(bp + (int64_t)iv * VEC), b);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = fmaf(o[i], g[i], b[i]);
+      } else if (gp != nullptr) {
         float g[VEC];
         unpack<TI, VEC>(ld_param<TI, VEC>(gp + (int64_t)iv * VEC), g);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) o[i] *= g[i];
-      }
-      if (bp != nullptr) {
+      } else if (bp != nullptr) {
         float b[VEC];
         unpack<TI, VEC>(ld_param<TI, VEC>(bp + (int64_t)iv * VEC), b);
 #pragma unroll
@@ -219,20 +251,20 @@ __global__ void __launch_bounds__(512) norm_fwd_generic_kernel(const FwdParams p
 // ----------------------------------------------------------------------------------------
 // dispatch
 // ----------------------------------------------------------------------------------------
-template <typename TI, typename TO, int VEC, int KIND, int ACT>
+template <typename TI, typename TO, int VEC, int KIND, int ACT, int FULL>
 static int launch_k(const FwdParams& p, const Plan& pl, int64_t grid, cudaStream_t st) {
   switch (pl.K) {
     case 1:
-      norm_fwd_kernel<TI, TO, VEC, 1, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      norm_fwd_kernel<TI, TO, VEC, 1, KIND, ACT, FULL><<<(unsigned)grid, pl.threads, 0, st>>>(p);
       break;
     case 2:
-      norm_fwd_kernel<TI, TO, VEC, 2, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      norm_fwd_kernel<TI, TO, VEC, 2, KIND, ACT, FULL><<<(unsigned)grid, pl.threads, 0, st>>>(p);
       break;
     case 4:
-      norm_fwd_kernel<TI, TO, VEC, 4, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      norm_fwd_kernel<TI, TO, VEC, 4, KIND, ACT, FULL><<<(unsigned)grid, pl.threads, 0, st>>>(p);
       break;
     case 8:
-      norm_fwd_kernel<TI, TO, VEC, 8, KIND, ACT><<<(unsigned)grid, pl.threads, 0, st>>>(p);
+      norm_fwd_kernel<TI, TO, VEC, 8, KIND, ACT, FULL><<<(unsigned)grid, pl.threads, 0, st>>>(p);
       break;
     default:
       return FLN_ERR_ARG;
@@ -257,8 +289,12 @@ static int launch_typed(FwdParams p, bool aligned, cudaStream_t st) {
   }
   p.nv = p.cols / pl.vec;
   const int64_t grid = (p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta;
-  if (pl.vec == FULL) return launch_k<TI, TO, FULL, KIND, ACT>(p, pl, grid, st);
-  return launch_k<TI, TO, 1, KIND, ACT>(p, pl, grid, st);
+  if (pl.vec == FULL) {
+    const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
+    return full ? launch_k<TI, TO, FULL, KIND, ACT, 1>(p, pl, grid, st)
+                : launch_k<TI, TO, FULL, KIND, ACT, 0>(p, pl, grid, st);
+  }
+  return launch_k<TI, TO, 1, KIND, ACT, 0>(p, pl, grid, st);
 }
 
 template <typename TI, typename TO>

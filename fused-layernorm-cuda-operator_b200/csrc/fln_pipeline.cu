@@ -109,12 +109,17 @@ __device__ __forceinline__ void pipeline_abort(uint64_t* full, int S, int s, uin
 // Statistics are the two-pass form on the row shifted by its first element, each pass
 // reduced by a warp butterfly plus one shared-memory hop.
 // ----------------------------------------------------------------------------------------
-template <typename TI, typename TO, int K, int KIND, int ACT, bool FULL>
+// MODE 0: general (bounds-checked); 1: FULL (no predication in the loop); 2: FULL and the
+// CTA owns exactly one row, which allows the one-barrier LayerNorm statistics below (measured
+// no faster on B200, so the launcher does not select it).
+template <typename TI, typename TO, int K, int KIND, int ACT, int MODE>
 __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = 16 / sizeof(TI);
+  constexpr bool FULL = MODE >= 1;
+  constexpr bool ONE = MODE == 2 && KIND == FLN_LAYERNORM;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  float* s_red = reinterpret_cast<float*>(smem + 256);  // 4 x 32 floats
+  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 + 2 x 32 floats
   unsigned char* stages = smem + kSmemHeader;
 
   const int tid = threadIdx.x;
@@ -177,8 +182,8 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     const bool landed = mbar_wait_bounded(&full[s], phase);
     const bool row_ok = FULL ? true : row < p.rows;
     const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
-    float* redA = s_red + (i & 1) * 32;
-    float* redB = s_red + 64 + (i & 1) * 32;
+    float* redA = s_red + (i & 1) * 64;
+    float* redB = s_red + 128 + (i & 1) * 32;
 
     float f[K][VEC];
 #pragma unroll
@@ -208,7 +213,8 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       }
     }
 
-    float mean = 0.f;
+    float mean = 0.f, rstd = 0.f;
+    bool need_second = true;  // is the exact centred pass needed
     if (KIND == FLN_LAYERNORM) {
       // shift by element 0 of the row (a broadcast read of the stage): a constant row then
       // sums to exactly zero whatever its magnitude, and |mean| >> std costs no accuracy
@@ -217,6 +223,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       if (has_res)
         c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0 + g.second_off))));
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four chains: the adds are latency-bound
+      float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         if (FULL || vok[k]) {  // padding vectors stay zero
@@ -230,11 +237,20 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
             a1 += f[k][e + 1];
             a2 += f[k][e + 2];
             a3 += f[k][e + 3];
+            if (ONE) {
+              b0 = fmaf(f[k][e], f[k][e], b0);
+              b1 = fmaf(f[k][e + 1], f[k][e + 1], b1);
+              b2 = fmaf(f[k][e + 2], f[k][e + 2], b2);
+              b3 = fmaf(f[k][e + 3], f[k][e + 3], b3);
+            }
           }
         }
       }
-      float a[1] = {(a0 + a1) + (a2 + a3)};
-      rowsum_warp<1>(a, tpr, redA);
+      constexpr int NA = ONE ? 2 : 1;
+      float ar[NA];
+      ar[0] = (a0 + a1) + (a2 + a3);
+      if (ONE) ar[NA - 1] = (b0 + b1) + (b2 + b3);
+      rowsum_warp<NA>(ar, tpr, redA);
       // The first barrier of a tile also proves that every thread has pulled its part of
       // stage s into registers, so the producer may refill the stage right after it.
       if (!__syncthreads_and(landed ? 1 : 0)) {
@@ -242,8 +258,8 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
         return;
       }
       if (tid == 0 && i + S < my_tiles) issue(i + S, s);
-      rowsum_cta<1>(a, tpr, redA);
-      const float ms = a[0] * inv_n;  // mean of the shifted row
+      rowsum_cta<NA>(ar, tpr, redA);
+      const float ms = ar[0] * inv_n;  // mean of the shifted row
       mean = c + ms;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
@@ -252,31 +268,45 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
           for (int e = 0; e < VEC; ++e) f[k][e] -= ms;
         }
       }
-    }
-    float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-#pragma unroll
-      for (int e = 0; e < VEC; e += 4) {
-        q0 = fmaf(f[k][e], f[k][e], q0);
-        q1 = fmaf(f[k][e + 1], f[k][e + 1], q1);
-        q2 = fmaf(f[k][e + 2], f[k][e + 2], q2);
-        q3 = fmaf(f[k][e + 3], f[k][e + 3], q3);
+      if (ONE) {
+        // One-pass variance of the shifted row, E[d^2] - E[d]^2.  Its relative error grows
+        // like eps * (1 + 2 ms^2 / var), so it is trusted only when the shift element lay
+        // within two standard deviations of the mean; otherwise the exact centred pass
+        // below runs.  The CTA owns one row here and ms, var1 are bit-identical in all its
+        // threads, so the branch (and the barrier inside it) is uniform.
+        const float var1 = fmaf(ar[NA - 1], inv_n, -ms * ms);
+        if (ms * ms <= 4.f * var1) {
+          need_second = false;
+          rstd = rsqrtf(var1 + eps);
+        }
       }
     }
-    float q[1] = {(q0 + q1) + (q2 + q3)};
-    rowsum_warp<1>(q, tpr, redB);
-    if (KIND == FLN_LAYERNORM) {
-      __syncthreads();
-    } else {
-      if (!__syncthreads_and(landed ? 1 : 0)) {
-        pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
-        return;
+    if (need_second) {
+      float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4) {
+          q0 = fmaf(f[k][e], f[k][e], q0);
+          q1 = fmaf(f[k][e + 1], f[k][e + 1], q1);
+          q2 = fmaf(f[k][e + 2], f[k][e + 2], q2);
+          q3 = fmaf(f[k][e + 3], f[k][e + 3], q3);
+        }
       }
-      if (tid == 0 && i + S < my_tiles) issue(i + S, s);
+      float q[1] = {(q0 + q1) + (q2 + q3)};
+      rowsum_warp<1>(q, tpr, redB);
+      if (KIND == FLN_LAYERNORM) {
+        __syncthreads();
+      } else {
+        if (!__syncthreads_and(landed ? 1 : 0)) {
+          pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
+          return;
+        }
+        if (tid == 0 && i + S < my_tiles) issue(i + S, s);
+      }
+      rowsum_cta<1>(q, tpr, redB);
+      rstd = rsqrtf(fmaf(q[0], inv_n, eps));
     }
-    rowsum_cta<1>(q, tpr, redB);
-    const float rstd = rsqrtf(fmaf(q[0], inv_n, eps));
 
     if (row_ok && lane_r == 0) {
       if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
@@ -598,10 +628,10 @@ static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
     if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                             \
     kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                         \
   }
-#define FLN_CASE(KK)                  \
-  case KK:                            \
-    if (P.full) FLN_LAUNCH(KK, true)  \
-    else FLN_LAUNCH(KK, false)        \
+#define FLN_CASE(KK)                                                \
+  case KK:                                                          \
+    if (P.full) FLN_LAUNCH(KK, 1)                                   \
+    else FLN_LAUNCH(KK, 0)                                          \
     break;
   switch (P.K) {
     FLN_CASE(1) FLN_CASE(2) FLN_CASE(4) FLN_CASE(8)

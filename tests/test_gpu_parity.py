@@ -466,3 +466,25 @@ def test_pipeline_gelu_and_downcast(path_override):
 
 def test_device_status_is_clean_after_everything():
     assert capi.lib().fln_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_pipeline_one_barrier_statistics_and_outlier_fallback(path_override, dtype):
+    """A CTA that owns one full row takes a one-barrier path whose variance is trusted only
+    when the row's first element is within two sigma of the mean; rows whose first element
+    is an outlier must fall back to the exact centred pass.  Both kinds of rows, plus rows
+    with |mean| >> std and constant rows, are checked against the oracle."""
+    path_override(2)
+    rows, cols = 640, 8192
+    x, gamma, beta, _, _ = U.make_inputs(77, rows, cols, dtype)
+    x = x.float()
+    x[::3, 0] += 60.0          # first element far outside the row's distribution
+    x[1::7] += 300.0           # |mean| >> std
+    x[5] = 1e4                 # constant row
+    x = x.to(dtype)
+    got = U.run_forward(x, gamma, beta)
+    want = O.norm_forward(x, gamma, beta)
+    U.assert_out_close(got["y"], want["y"], dtype)
+    torch.testing.assert_close(got["mean"], want["mean"], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+    assert capi.lib().fln_device_status() == 0
