@@ -1,0 +1,182 @@
+"""torch.library registrations for the operators the extension defines (fused_layernorm::*).
+
+The C++ side (csrc/fln_torch_shim.cpp) declares the schemas and the CUDA implementations; this
+module adds what tracing needs: a fake (meta) implementation per operator, so torch.compile /
+make_fx can propagate shapes without running a kernel, and autograd formulas for the forward
+operators, expressed with the backward operators.  The reference wires autograd by hand in
+FusedLayerNormFunction (fused_layernorm/layernorm.py:31-109 of the reference) and registers no
+operators at all; its pybind functions are opaque to torch.compile.
+"""
+from __future__ import annotations
+
+import torch
+
+import fused_layernorm_cuda  # noqa: F401  (loads the TORCH_LIBRARY block; raises if not built)
+
+ops = torch.ops.fused_layernorm
+LAYERNORM, RMSNORM = 0, 1
+
+
+def _stat(x):
+    return x.new_empty((x.shape[0],), dtype=torch.float32)
+
+
+def _none_if_empty(t):
+    return None if t is None or t.numel() == 0 else t
+
+
+# ------------------------------------------------------------------------------------ fakes
+@torch.library.register_fake("fused_layernorm::layernorm")
+def _(input, gamma, beta, epsilon):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake("fused_layernorm::layernorm_gelu")
+def _(input, gamma, beta, epsilon, approximate):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake("fused_layernorm::layernorm_fwd")
+def _(input, gamma, beta, epsilon):
+    return torch.empty_like(input, memory_format=torch.contiguous_format), _stat(input), _stat(input)
+
+
+@torch.library.register_fake("fused_layernorm::rmsnorm_fwd")
+def _(input, gamma, epsilon):
+    return torch.empty_like(input, memory_format=torch.contiguous_format), _stat(input)
+
+
+@torch.library.register_fake("fused_layernorm::add_layernorm_fwd")
+def _(input, residual, gamma, beta, epsilon):
+    e = lambda: torch.empty_like(input, memory_format=torch.contiguous_format)
+    return e(), e(), _stat(input), _stat(input)
+
+
+@torch.library.register_fake("fused_layernorm::add_rmsnorm_fwd")
+def _(input, residual, gamma, epsilon):
+    e = lambda: torch.empty_like(input, memory_format=torch.contiguous_format)
+    return e(), e(), _stat(input)
+
+
+@torch.library.register_fake("fused_layernorm::norm_fp8")
+def _(kind, input, residual, gamma, beta, epsilon):
+    q = input.new_empty(input.shape, dtype=torch.float8_e4m3fn)
+    s = torch.empty_like(input, memory_format=torch.contiguous_format) if residual is not None else input.new_empty((0,))
+    mean = _stat(input) if kind == LAYERNORM else input.new_empty((0,), dtype=torch.float32)
+    return q, s, input.new_empty((1,), dtype=torch.float32), mean, _stat(input)
+
+
+@torch.library.register_fake("fused_layernorm::layernorm_bwd")
+def _(grad_output, input, mean, rstd, gamma, dres_in, need_dx, need_dgamma, need_dbeta):
+    cols = input.shape[1]
+    dx = torch.empty_like(input, memory_format=torch.contiguous_format) if (need_dx or dres_in is not None) \
+        else input.new_empty((0,))
+    return dx, input.new_empty((cols if need_dgamma else 0,)), input.new_empty((cols if need_dbeta else 0,))
+
+
+@torch.library.register_fake("fused_layernorm::rmsnorm_bwd")
+def _(grad_output, input, rstd, gamma, dres_in, need_dx, need_dgamma):
+    cols = input.shape[1]
+    dx = torch.empty_like(input, memory_format=torch.contiguous_format) if (need_dx or dres_in is not None) \
+        else input.new_empty((0,))
+    return dx, input.new_empty((cols if need_dgamma else 0,))
+
+
+@torch.library.register_fake("fused_layernorm::layernorm_bwd_f32")
+def _(grad_output, input, mean, rstd, gamma):
+    return torch.empty_like(input, memory_format=torch.contiguous_format), \
+        input.new_empty((2 * input.shape[1],), dtype=torch.float32)
+
+
+@torch.library.register_fake("fused_layernorm::cast_from_f32")
+def _(src, dtype):
+    return src.new_empty(src.shape, dtype=dtype)
+
+
+# --------------------------------------------------------------------------------- autograd
+# Gradients flow through y (and through the residual sum for the fused-add forms); the saved
+# statistics are not differentiable outputs.
+def _ln_setup(ctx, inputs, output):
+    input, gamma, beta, _eps = inputs
+    _y, mean, rstd = output
+    ctx.save_for_backward(input, gamma, mean, rstd)
+    ctx.has_beta = beta is not None
+    ctx.set_materialize_grads(False)
+
+
+def _ln_backward(ctx, gy, _gmean, _grstd):
+    input, gamma, mean, rstd = ctx.saved_tensors
+    if gy is None:
+        return None, None, None, None
+    need = ctx.needs_input_grad
+    dx, dg, db = ops.layernorm_bwd(gy, input, mean, rstd, gamma, None, need[0], need[1] and gamma is not None,
+                                   need[2] and ctx.has_beta)
+    return _none_if_empty(dx), _none_if_empty(dg), _none_if_empty(db), None
+
+
+torch.library.register_autograd("fused_layernorm::layernorm_fwd", _ln_backward, setup_context=_ln_setup)
+
+
+def _rms_setup(ctx, inputs, output):
+    input, gamma, _eps = inputs
+    _y, rstd = output
+    ctx.save_for_backward(input, gamma, rstd)
+    ctx.set_materialize_grads(False)
+
+
+def _rms_backward(ctx, gy, _grstd):
+    input, gamma, rstd = ctx.saved_tensors
+    if gy is None:
+        return None, None, None
+    need = ctx.needs_input_grad
+    dx, dg = ops.rmsnorm_bwd(gy, input, rstd, gamma, None, need[0], need[1] and gamma is not None)
+    return _none_if_empty(dx), _none_if_empty(dg), None
+
+
+torch.library.register_autograd("fused_layernorm::rmsnorm_fwd", _rms_backward, setup_context=_rms_setup)
+
+
+def _addln_setup(ctx, inputs, output):
+    _input, _residual, gamma, beta, _eps = inputs
+    _y, s, mean, rstd = output
+    ctx.save_for_backward(s, gamma, mean, rstd)
+    ctx.has_beta = beta is not None
+    ctx.set_materialize_grads(False)
+
+
+def _addln_backward(ctx, gy, gsum, _gmean, _grstd):
+    s, gamma, mean, rstd = ctx.saved_tensors
+    need = ctx.needs_input_grad
+    if gy is None:
+        d = gsum
+        return (d if need[0] else None), (d if need[1] else None), None, None, None
+    want_dx = need[0] or need[1]
+    dx, dg, db = ops.layernorm_bwd(gy, s, mean, rstd, gamma, gsum if want_dx else None, want_dx,
+                                   need[2] and gamma is not None, need[3] and ctx.has_beta)
+    dx = _none_if_empty(dx)
+    return (dx if need[0] else None), (dx if need[1] else None), _none_if_empty(dg), _none_if_empty(db), None
+
+
+torch.library.register_autograd("fused_layernorm::add_layernorm_fwd", _addln_backward, setup_context=_addln_setup)
+
+
+def _addrms_setup(ctx, inputs, output):
+    _input, _residual, gamma, _eps = inputs
+    _y, s, rstd = output
+    ctx.save_for_backward(s, gamma, rstd)
+    ctx.set_materialize_grads(False)
+
+
+def _addrms_backward(ctx, gy, gsum, _grstd):
+    s, gamma, rstd = ctx.saved_tensors
+    need = ctx.needs_input_grad
+    if gy is None:
+        d = gsum
+        return (d if need[0] else None), (d if need[1] else None), None, None
+    want_dx = need[0] or need[1]
+    dx, dg = ops.rmsnorm_bwd(gy, s, rstd, gamma, gsum if want_dx else None, want_dx, need[2] and gamma is not None)
+    dx = _none_if_empty(dx)
+    return (dx if need[0] else None), (dx if need[1] else None), _none_if_empty(dg), None
+
+
+torch.library.register_autograd("fused_layernorm::add_rmsnorm_fwd", _addrms_backward, setup_context=_addrms_setup)

@@ -1,0 +1,97 @@
+"""RMSNorm, fused residual-add + norm, and fp8-e4m3 output: the siblings of the LayerNorm path.
+
+The reference has none of these (it ships LayerNorm and LayerNorm+GELU forward only,
+csrc/bindings.cpp:41-44 of the reference); their semantics are the plain-torch compositions
+    s = x + residual                      (rounded to the tensor dtype, as an unfused add would)
+    y = rms_norm(s) or layer_norm(s)      (fp32 statistics, one rounding on store)
+    q = (y * 448 / max|y|).to(float8_e4m3fn)
+All functions take tensors of any rank and normalize over the last dimension.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+from torch.nn import Parameter
+
+from . import ops as _ops  # noqa: F401
+from .layernorm import _require_cuda
+
+_t = torch.ops.fused_layernorm
+
+
+def _flat(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+def fused_rms_norm(input: torch.Tensor, weight: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * weight over the last dimension (differentiable)."""
+    _require_cuda(input)
+    y, _rstd = _t.rmsnorm_fwd(_flat(input), weight, eps)
+    return y.reshape(input.shape)
+
+
+def fused_add_layer_norm(input: torch.Tensor, residual: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                         bias: Optional[torch.Tensor] = None, eps: float = 1e-5) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(layer_norm(input + residual), input + residual) in one pass over HBM (differentiable;
+    a gradient arriving on the returned sum is added into the input gradient by the kernel)."""
+    _require_cuda(input)
+    y, s, _mean, _rstd = _t.add_layernorm_fwd(_flat(input), _flat(residual), weight, bias, eps)
+    return y.reshape(input.shape), s.reshape(input.shape)
+
+
+def fused_add_rms_norm(input: torch.Tensor, residual: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                       eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(rms_norm(input + residual), input + residual) in one pass over HBM (differentiable)."""
+    _require_cuda(input)
+    y, s, _rstd = _t.add_rmsnorm_fwd(_flat(input), _flat(residual), weight, eps)
+    return y.reshape(input.shape), s.reshape(input.shape)
+
+
+def fused_add_rms_norm_fp8(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                           weight: Optional[torch.Tensor] = None, eps: float = 1e-6):
+    """(q, sum, scale): q = rms_norm(input + residual) quantized to float8_e4m3fn with the
+    per-tensor scale 448 / max|y| computed on the device; sum = input + residual (None when
+    residual is None); scale is a 1-element fp32 tensor (dequantize with q.float() / scale).
+    Forward only."""
+    _require_cuda(input)
+    q, s, scale, _mean, _rstd = _t.norm_fp8(_ops.RMSNORM, _flat(input), None if residual is None else _flat(residual),
+                                            weight, None, eps)
+    return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), scale
+
+
+def fused_add_layer_norm_fp8(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                             weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                             eps: float = 1e-5):
+    """LayerNorm variant of fused_add_rms_norm_fp8."""
+    _require_cuda(input)
+    q, s, scale, _mean, _rstd = _t.norm_fp8(_ops.LAYERNORM, _flat(input), None if residual is None else _flat(residual),
+                                            weight, bias, eps)
+    return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), scale
+
+
+class FusedRMSNorm(nn.Module):
+    """torch.nn.RMSNorm-compatible module (normalized_shape, eps, elementwise_affine; parameter `weight`)."""
+
+    def __init__(self, normalized_shape, eps: Optional[float] = None, elementwise_affine: bool = True,
+                 device=None, dtype=None) -> None:
+        super().__init__()
+        if isinstance(normalized_shape, int):
+            normalized_shape = (normalized_shape,)
+        self.normalized_shape = tuple(normalized_shape)
+        if len(self.normalized_shape) != 1:
+            raise ValueError("FusedRMSNorm normalizes over the last dimension only")
+        self.eps = eps
+        self.elementwise_affine = elementwise_affine
+        if elementwise_affine:
+            self.weight = Parameter(torch.ones(self.normalized_shape, device=device, dtype=dtype))
+        else:
+            self.register_parameter("weight", None)
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        eps = self.eps if self.eps is not None else torch.finfo(input.dtype).eps
+        return fused_rms_norm(input, self.weight, eps)
+
+    def extra_repr(self) -> str:
+        return "{normalized_shape}, eps={eps}, elementwise_affine={elementwise_affine}".format(**self.__dict__)

@@ -1,0 +1,114 @@
+"""Row-sharded LayerNorm forward + backward across the GPUs of one node.
+
+Rows are independent, so a batch of `total_rows` rows is cut into contiguous, near-equal
+shards, one per rank; gamma / beta are replicated.  The forward needs no communication.  The
+backward needs exactly one exchange: the per-rank fp32 partial sums [dgamma | dbeta] (one
+contiguous buffer of 2 * hidden floats, written by the column-reduction kernel with no
+rounding) are summed with a single all-reduce, and only then rounded to the parameter dtype.
+On GPUs the process group is NCCL (NVLink / NVSwitch); the reference has no multi-GPU code
+at all.  Nothing here puts kernels of different ranks on one GPU or waits on a peer from
+inside a kernel: the only cross-rank synchronization is the collective itself.
+
+The local computation is injected (`backend`) so that the sharding / reduction logic can be
+exercised on CPU ranks over gloo with a checker as the backend; the default backend is the
+CUDA operator set and raises if the extension is missing.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(total_rows: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """[start, end) of rank's shard: ceil-split, later ranks may get fewer (or zero) rows."""
+    if total_rows < 0 or world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError(f"bad sharding request: rows={total_rows} world={world_size} rank={rank}")
+    per = -(-total_rows // world_size)
+    start = min(rank * per, total_rows)
+    return start, min(start + per, total_rows)
+
+
+class CudaBackend:
+    """Local compute on the current CUDA device through the registered operators."""
+
+    def __init__(self):
+        from . import ops as _ops  # noqa: F401  (raises ImportError when the extension is missing)
+        self._t = torch.ops.fused_layernorm
+
+    def forward(self, x, gamma, beta, eps):
+        return self._t.layernorm_fwd(x, gamma, beta, eps)
+
+    def backward_f32(self, dy, x, mean, rstd, gamma):
+        return self._t.layernorm_bwd_f32(dy, x, mean, rstd, gamma)
+
+    def cast(self, f32, dtype):
+        return self._t.cast_from_f32(f32, dtype)
+
+
+class ShardedLayerNorm:
+    """forward / backward of one rank's shard, plus the all-reduce of the parameter gradients.
+
+        sln = ShardedLayerNorm(hidden, eps)            # after dist.init_process_group(...)
+        y, saved = sln.forward(x_shard, gamma, beta)
+        dx, dgamma, dbeta = sln.backward(dy_shard, saved, gamma)
+    """
+
+    def __init__(self, hidden: int, eps: float = 1e-5, group=None, backend=None):
+        self.hidden = int(hidden)
+        self.eps = float(eps)
+        self.group = group
+        self.backend = backend if backend is not None else CudaBackend()
+
+    # -- checks that run on the host before anything is launched -------------------------
+    def _check_shard(self, t: torch.Tensor, name: str):
+        if t.dim() != 2 or t.shape[1] != self.hidden:
+            raise ValueError(f"{name} must be [rows, {self.hidden}], got {tuple(t.shape)}")
+
+    def validate(self, local_rows: int, total_rows: Optional[int] = None):
+        """Collective sanity check (call it once, not per step): every rank uses the same
+        hidden size and, when total_rows is given, the shard sizes are those of shard_bounds."""
+        world = dist.get_world_size(self.group)
+        rank = dist.get_rank(self.group)
+        mine = torch.tensor([self.hidden, local_rows], dtype=torch.int64)
+        if dist.get_backend(self.group) == "nccl":
+            mine = mine.cuda()
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine, group=self.group)
+        hs = [int(g[0]) for g in gathered]
+        rows = [int(g[1]) for g in gathered]
+        if len(set(hs)) != 1:
+            raise RuntimeError(f"hidden size differs across ranks: {hs}")
+        if total_rows is not None:
+            want = [shard_bounds(total_rows, world, r) for r in range(world)]
+            if rows != [b - a for a, b in want]:
+                raise RuntimeError(f"shard sizes {rows} do not match an even split of {total_rows} rows over {world} ranks")
+        return rows[rank]
+
+    # -- the path ------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor]):
+        self._check_shard(x, "x")
+        y, mean, rstd = self.backend.forward(x, gamma, beta, self.eps)
+        return y, (x, mean, rstd)
+
+    def backward(self, dy: torch.Tensor, saved, gamma: Optional[torch.Tensor], async_op: bool = False):
+        """Returns (dx, dgamma, dbeta); dgamma / dbeta are the sums over ALL ranks' rows, in the
+        dtype of x.  With async_op=True returns (dx, finish) where finish() waits for the
+        all-reduce and returns (dgamma, dbeta), so the caller can overlap it with other work."""
+        x, mean, rstd = saved
+        self._check_shard(dy, "dy")
+        if dy.shape != x.shape:
+            raise ValueError(f"dy shape {tuple(dy.shape)} does not match x shape {tuple(x.shape)}")
+        dx, dgb = self.backend.backward_f32(dy, x, mean, rstd, gamma)  # dgb: fp32 [2 * hidden], zeros for an empty shard
+        work = dist.all_reduce(dgb, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        def finish():
+            work.wait()
+            out = self.backend.cast(dgb, x.dtype)
+            return out[: self.hidden], out[self.hidden:]
+
+        if async_op:
+            return dx, finish
+        dgamma, dbeta = finish()
+        return dx, dgamma, dbeta
