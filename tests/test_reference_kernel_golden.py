@@ -1,0 +1,98 @@
+"""Pins against outputs of the reference's OWN shipped CUDA kernels.
+
+tests/golden/ref_g2_b200.npz holds what fused_layernorm_cuda.layernorm / layernorm_gelu of the
+reference (compiled unmodified for sm_100 by oracle/build_ref.py) produced on a B200 for
+seeded inputs (generator: tests/golden/make_ref_g2_golden.py).  Checked here:
+  * CPU: the literal restatement of that kernel in oracle/fln_oracle.c (ref_g2_layernorm_f32)
+    reproduces it to fp32 round-off, and the double-accumulator oracle agrees at 1e-5;
+  * GPU: this repository's kernels agree with the reference's outputs at 1e-5 abs/rel, and,
+    when the reference extension is present (oracle/_ref), on fresh inputs as well.
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+ROOT = Path(__file__).resolve().parents[1]
+Z = np.load(ROOT / "tests" / "golden" / "ref_g2_b200.npz")
+CASES = sorted({k.split("/")[0] for k in Z.files if not k.startswith("meta")})
+
+
+def case(name):
+    return {k: torch.from_numpy(Z[f"{name}/{k}"].copy()) for k in ("x", "gamma", "beta", "y", "y_gelu")}
+
+
+def test_fixture_came_from_a_b200():
+    assert "B200" in str(Z["meta/device"]) and len(CASES) == 7
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_literal_restatement_reproduces_reference_kernel(name):
+    c = case(name)
+    y = O.ref_g2_layernorm(c["x"], c["gamma"], c["beta"], 1e-5, gelu=False)
+    yg = O.ref_g2_layernorm(c["x"], c["gamma"], c["beta"], 1e-5, gelu=True)
+    # same algorithm, same summation order; what is left is rsqrtf / tanhf device round-off
+    torch.testing.assert_close(y, c["y"], rtol=2e-6, atol=2e-6 * float(c["y"].abs().max()))
+    torch.testing.assert_close(yg, c["y_gelu"], rtol=2e-6, atol=2e-6 * float(c["y"].abs().max()))
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_truth_oracle_agrees_with_reference_kernel(name):
+    c = case(name)
+    tol = 1e-5 if "x1000" not in name else 1e-4   # the reference's own wide-range tolerance (rtol 1e-4)
+    y = O.norm_forward(c["x"], c["gamma"], c["beta"])["y"]
+    yg = O.norm_forward(c["x"], c["gamma"], c["beta"], act="gelu_tanh")["y"]
+    torch.testing.assert_close(y, c["y"], rtol=tol, atol=1e-5)
+    torch.testing.assert_close(yg, c["y_gelu"], rtol=tol, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_our_kernels_match_reference_kernel_outputs(name):
+    import fused_layernorm_cuda
+    c = case(name)
+    tol = 1e-5 if "x1000" not in name else 1e-4
+    x, g, b = c["x"].cuda(), c["gamma"].cuda(), c["beta"].cuda()
+    torch.testing.assert_close(fused_layernorm_cuda.layernorm(x, g, b, 1e-5).cpu(), c["y"], rtol=tol, atol=1e-5)
+    torch.testing.assert_close(fused_layernorm_cuda.layernorm_gelu(x, g, b, 1e-5).cpu(), c["y_gelu"], rtol=tol, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_side_by_side_with_reference_extension_when_present():
+    """Fresh inputs through both extensions on the same GPU, and the same-tensor loop timing
+    protocol of the reference (benchmarks/reproduce_speedup.py:46-77): ours must not be slower."""
+    ref_dir = ROOT / "oracle" / "_ref"
+    if not list(ref_dir.glob("ref_g2_layernorm_cuda*.so")):
+        pytest.skip("reference extension not built (oracle/build_ref.py needs the reference checkout)")
+    sys.path.insert(0, str(ref_dir))
+    import fused_layernorm_cuda
+    import ref_g2_layernorm_cuda as ref
+    out = {}
+    for rows, cols in [(32, 768), (32, 1024), (32, 4096), (64, 4096), (17, 1023)]:
+        x = torch.randn(rows, cols, device="cuda") * 3 + 0.5
+        g = 1 + 0.1 * torch.randn(cols, device="cuda")
+        b = 0.1 * torch.randn(cols, device="cuda")
+        torch.testing.assert_close(fused_layernorm_cuda.layernorm(x, g, b, 1e-5), ref.layernorm(x, g, b, 1e-5),
+                                   rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(fused_layernorm_cuda.layernorm_gelu(x, g, b, 1e-5), ref.layernorm_gelu(x, g, b, 1e-5),
+                                   rtol=1e-5, atol=1e-5)
+        t = {}
+        for name, fn in (("ours", fused_layernorm_cuda.layernorm), ("reference", ref.layernorm)):
+            for _ in range(200):
+                fn(x, g, b, 1e-5)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(1000):
+                fn(x, g, b, 1e-5)
+            e1.record()
+            torch.cuda.synchronize()
+            t[name] = e0.elapsed_time(e1)  # us per call
+        out[f"{rows}x{cols}"] = t
+    print("us/call, same-tensor loop:", out)
+    for shape, t in out.items():
+        assert t["ours"] <= t["reference"] * 1.15, (shape, t)
