@@ -150,32 +150,18 @@ def run_reference(args, rank):
 
 
 def small_shape_latency(torch, capi):
-    """us/call at 32 x 4096 fp32 (the reference's README shape): same-tensor back-to-back
-    loop, eager C-ABI launches vs one CUDA-graph launch per call vs torch's own CUDA op."""
+    """us/call for the latency-bound sweep (32x768 fp32 and the 32x1024 / 32x4096 / 64x4096 /
+    17x1023 shapes, fp32 and bf16), with the reference's own protocol: same-tensor back-to-back
+    loop of 1000 calls after 200 warm-ups, CUDA events around the loop.  Columns: the pybind
+    entry point a user of the reference calls (allocates its output), the raw C-ABI launch,
+    one CUDA-graph launch per call, a graph holding 20 calls (per call), and torch's own CUDA
+    LayerNorm."""
     import torch.nn.functional as F
-    out = {}
-    x = torch.randn(32, 4096, device="cuda")
-    w = torch.ones(4096, device="cuda")
-    b = torch.zeros(4096, device="cuda")
-    y = torch.empty_like(x)
+    import fused_layernorm_cuda as ext
+    from fused_layernorm.graphs import GraphedLayerNorm
     L = capi.lib()
-    px, pw, pb, py = capi.ptr(x), capi.ptr(w), capi.ptr(b), capi.ptr(y)
-    st = capi.stream_handle()
 
-    def eager():
-        L.fln_layernorm_forward(px, pw, pb, py, None, None, 32, 4096, 0, 1e-5, st)
-
-    g = capi.Graph()
-    with g.record() as s:
-        capi.layernorm_forward(x, w, b, y, None, None, 1e-5, stream=s)
-
-    def graph():
-        L.fln_graph_launch(g._h, st)
-
-    def torch_native():
-        F.layer_norm(x, (4096,), w, b, 1e-5)
-
-    for name, fn in (("ours_eager_us", eager), ("ours_graph_us", graph), ("torch_cuda_us", torch_native)):
+    def loop_us(fn, calls_per_iter=1):
         for _ in range(200):
             fn()
         torch.cuda.synchronize()
@@ -185,9 +171,33 @@ def small_shape_latency(torch, capi):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        out[name] = e0.elapsed_time(e1)  # ms per 1000 calls == us per call
-    g.close()
-    out["shape"] = "32x4096 fp32, same-tensor loop of 1000 calls"
+        return e0.elapsed_time(e1) / calls_per_iter  # ms per 1000 iterations == us per iteration
+
+    out = {"protocol": "same-tensor loop, 200 warm-up + 1000 timed calls, us per call"}
+    shapes = [(32, 768, torch.float32)] + [(r, c, dt) for dt in (torch.float32, torch.bfloat16)
+                                           for r, c in ((32, 1024), (32, 4096), (64, 4096), (17, 1023))]
+    for rows, cols, dt in shapes:
+        x = (torch.randn(rows, cols, device="cuda") * 3 + 0.5).to(dt)
+        w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(dt)
+        b = (0.1 * torch.randn(cols, device="cuda")).to(dt)
+        y = torch.empty_like(x)
+        px, pw, pb, py, st = capi.ptr(x), capi.ptr(w), capi.ptr(b), capi.ptr(y), capi.stream_handle()
+        code = capi.DTYPES[dt]
+        g1 = GraphedLayerNorm(x, w, b, 1e-5)
+        g20 = GraphedLayerNorm(x, w, b, 1e-5, repeat=20)
+        gg = GraphedLayerNorm(x, w, b, 1e-5, gelu="tanh", repeat=20)
+        rec = {
+            "ours_pybind": loop_us(lambda: ext.layernorm(x, w, b, 1e-5)),
+            "ours_pybind_gelu": loop_us(lambda: ext.layernorm_gelu(x, w, b, 1e-5)),
+            "ours_c_abi": loop_us(lambda: L.fln_layernorm_forward(px, pw, pb, py, None, None, rows, cols, code, 1e-5, st)),
+            "ours_graph": loop_us(lambda: g1()),
+            "ours_graph_x20": loop_us(lambda: g20(), 20),
+            "ours_graph_x20_gelu": loop_us(lambda: gg(), 20),
+            "torch_cuda": loop_us(lambda: F.layer_norm(x, (cols,), w, b, 1e-5)),
+        }
+        for g in (g1, g20, gg):
+            g.close()
+        out[f"{rows}x{cols}_{str(dt).replace('torch.', '')}"] = {k: round(v, 2) for k, v in rec.items()}
     return out
 
 
@@ -323,10 +333,13 @@ def run_ours(args):
         "rows_per_s": rows * world / (ms_per_step * 1e-3),
         "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
         "frac_of_" + peak_src: value / world / peak,
-        "roofline": {"kernel": "norm_bwd_kernel + colreduce_kernel (backward)", "bound": "hbm", "achieved": bwd_gbs,
-                     "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None, "peak_source": peak_src,
+        "roofline": {"kernel": "norm_bwd_pipe_kernel (+ colreduce_kernel, < 2 % of the time)", "bound": "hbm", "achieved": bwd_gbs,
+                     "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch
+                     # (profiles/norm_bwd_pipe_kernel_16384x8192_bf16.md); only for the default workload
+                     "traffic": 769.4e6 if (rows, cols) == (16384, 8192) else None, "peak_source": peak_src,
                      "algorithmic_bytes": bwd_b, "avg_ms": bwd_ms},
-        "roofline_forward": {"kernel": "norm_fwd_kernel", "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
+        "roofline_forward": {"kernel": "norm_fwd_pipe_kernel", "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
                              "unit": "GB/s", "frac": fwd_gbs / peak, "algorithmic_bytes": fwd_b, "avg_ms": fwd_ms},
         "clocks": clocks, "gpu_launches": K * launches_per_step,
     }
