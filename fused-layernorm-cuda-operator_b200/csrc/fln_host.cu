@@ -162,6 +162,9 @@ extern "C" const char* fln_status_string(int status) {
       return "CUDA graph operation failed";
     case FLN_ERR_ARG:
       return "invalid argument";
+    case FLN_ERR_STATIC_SCRATCH:
+      return "problem needs more scratch than the built-in static array holds (FLN_STATIC_SCRATCH_BYTES); "
+             "use fln_layernorm_backward with a caller-provided workspace";
   }
   return "unknown status";
 }

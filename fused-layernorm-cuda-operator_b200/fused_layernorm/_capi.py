@@ -28,8 +28,9 @@ SYMBOLS = [
     "fln_backward_workspace_bytes", "fln_layernorm_backward", "fln_norm_backward", "fln_cast_from_f32",
     "fln_graph_begin", "fln_graph_stream", "fln_graph_end", "fln_graph_launch", "fln_graph_destroy",
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
-    "fln_set_path_override", "fln_device_status",
+    "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static",
 ]
+STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
 
 class LaunchInfo(C.Structure):
@@ -80,6 +81,7 @@ def lib() -> C.CDLL:
     L.fln_set_path_override.argtypes = [i32]
     L.fln_set_path_override.restype = None
     L.fln_device_status.restype = i32
+    L.fln_layernorm_backward_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp]
     _lib = L
     return L
 
@@ -155,6 +157,17 @@ def layernorm_backward(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace, s
     check(lib().fln_layernorm_backward(ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dx),
                                        ptr(dgamma), ptr(dbeta), ptr(workspace), ws_bytes, rows, cols,
                                        dtype_code(x), stream_handle(stream)), "fln_layernorm_backward")
+
+
+def layernorm_backward_static(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, stream=None):
+    """LayerNorm backward for hosts that may not allocate device memory: no workspace argument,
+    the partial sums live in an array built into the library (at most STATIC_SCRATCH_BYTES;
+    larger problems raise).  Make the first call on a device outside stream capture, and do
+    not let two calls overlap on the GPU: they share that array."""
+    rows, cols = x.shape
+    check(lib().fln_layernorm_backward_static(ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dx),
+                                              ptr(dgamma), ptr(dbeta), rows, cols, dtype_code(x),
+                                              stream_handle(stream)), "fln_layernorm_backward_static")
 
 
 def cast_from_f32(src, dst, stream=None):

@@ -45,7 +45,8 @@ typedef enum {
   FLN_ERR_LAUNCH = 5,      /* the CUDA runtime reported an error at launch       */
   FLN_ERR_UNSUPPORTED = 6, /* combination not implemented (e.g. fp8 with odd cols) */
   FLN_ERR_GRAPH = 7,       /* CUDA-graph capture / instantiate / launch failed   */
-  FLN_ERR_ARG = 8          /* bad enum value or inconsistent arguments           */
+  FLN_ERR_ARG = 8,         /* bad enum value or inconsistent arguments           */
+  FLN_ERR_STATIC_SCRATCH = 9 /* problem too large for the built-in scratch array  */
 } fln_status;
 
 /* Human-readable text for a status code (static storage). */
@@ -143,6 +144,28 @@ int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean
                       void* dgamma, void* dbeta, float* dgb_f32, void* workspace,
                       size_t workspace_bytes, int64_t rows, int64_t cols, int dtype,
                       void* stream);
+
+/* LayerNorm backward that allocates nothing and asks the caller for no scratch either.
+ * It has no counterpart in the reference.  It exists for hosts that must not allocate device
+ * memory once they are running: runtimes with a fixed memory plan (all device memory is
+ * handed out at start-up), loops that cannot tolerate the device-wide synchronization of
+ * cudaMalloc / cudaFree, plain C callers without a caching allocator.  Same arguments and
+ * results as fln_layernorm_backward minus the workspace pair; the partial sums go to a
+ * built-in __device__ array of FLN_STATIC_SCRATCH_BYTES that every GPU which loads the library
+ * holds until the process exits.
+ *   - Problems whose fln_backward_workspace_bytes() exceeds FLN_STATIC_SCRATCH_BYTES are
+ *     refused with FLN_ERR_STATIC_SCRATCH and nothing is launched.
+ *   - The first call made on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps the last call's contents.  Nothing in it has
+ *     to be zero beforehand (every partial row that is read is written first), but two calls
+ *     that overlap on the GPU -- different streams, or graphs replayed concurrently -- race on
+ *     it; serialize them.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine. */
+#define FLN_STATIC_SCRATCH_BYTES (16u << 20)
+int fln_layernorm_backward_static(const void* dy, const void* x, const float* mean,
+                                  const float* rstd, const void* gamma, void* dx, void* dgamma,
+                                  void* dbeta, int64_t rows, int64_t cols, int dtype, void* stream);
 
 /* dst[i] = (dtype) src[i] for n fp32 values: turns an all-reduced dgb_f32 buffer into
  * parameter-typed gradients.  No counterpart in the reference. */
