@@ -423,7 +423,7 @@ def path_override():
     capi.lib().fln_set_path_override(0)
 
 
-@pytest.mark.parametrize("mode", [1, 2])  # 1 = register-resident kernels, 2 = bulk-async pipeline
+@pytest.mark.parametrize("mode", [1, 2, 4])  # 1 = register kernels, 2 = bulk-async pipeline, 4 = + two-row backward
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype", [F32, BF16, F16])
 @pytest.mark.parametrize("shape", [(701, 4096), (333, 8192), (1500, 768), (2049, 1024), (97, 16384), (4099, 256)])
