@@ -81,6 +81,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// One 16-byte vector of a stage as ONE 128-bit shared-memory load.  (Handing the stage to the
+// conversion helper by reference lets the compiler read it word by word: four times the load
+// instructions and the shared-memory pipe becomes the stall.)
+template <typename T>
+__device__ __forceinline__ Pack<T, 16 / sizeof(T)> ld_smem16(const unsigned char* p) {
+  Pack<T, 16 / sizeof(T)> out;
+  *reinterpret_cast<uint4*>(&out) = *reinterpret_cast<const uint4*>(p);
+  return out;
+}
+
 // tiles of CTA b: t = b + i * gridDim.x  (evaluated once per CTA)
 __device__ __forceinline__ int my_tile_count(int64_t n_tiles) {
   return (int64_t)blockIdx.x < n_tiles ? (int)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
@@ -189,7 +199,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<TI, VEC>(*reinterpret_cast<const Pack<TI, VEC>*>(st + k * k_off), f[k]);
+        unpack<TI, VEC>(ld_smem16<TI>(st + k * k_off), f[k]);
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) f[k][e] = 0.f;
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       for (int k = 0; k < K; ++k) {
         if (FULL || (row_ok && vok[k])) {
           float r[VEC];
-          unpack<TI, VEC>(*reinterpret_cast<const Pack<TI, VEC>*>(st + g.second_off + k * k_off), r);
+          unpack<TI, VEC>(ld_smem16<TI>(st + g.second_off + k * k_off), r);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) f[k][e] += r[e];
           // the sum is rounded to the I/O type first: that value is normalized and stored
@@ -423,8 +433,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + k * k_off), dyf[k]);
-        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + g.second_off + k * k_off), xh[k]);
+        unpack<T, VEC>(ld_smem16<T>(st + k * k_off), dyf[k]);
+        unpack<T, VEC>(ld_smem16<T>(st + g.second_off + k * k_off), xh[k]);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) xh[k][e] = (xh[k][e] - mean) * rstd;
       } else {
@@ -609,8 +619,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe2_kernel(const BwdParams p, 
       float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + rr * rr_off + k * k_off), dyf[rr][k]);
-        unpack<T, VEC>(*reinterpret_cast<const Pack<T, VEC>*>(st + g.second_off + rr * rr_off + k * k_off), xh[rr][k]);
+        unpack<T, VEC>(ld_smem16<T>(st + rr * rr_off + k * k_off), dyf[rr][k]);
+        unpack<T, VEC>(ld_smem16<T>(st + g.second_off + rr * rr_off + k * k_off), xh[rr][k]);
 #pragma unroll
         for (int e = 0; e < VEC; e += 2) {
           xh[rr][k][e] = (xh[rr][k][e] - mean[rr]) * rstd[rr];
