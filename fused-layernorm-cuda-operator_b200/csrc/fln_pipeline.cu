@@ -91,6 +91,19 @@ __device__ __forceinline__ Pack<T, 16 / sizeof(T)> ld_smem16(const unsigned char
   return out;
 }
 
+// How a kernel takes one vector out of a stage.  16-bit types: by value through the 128-bit
+// load above (measured 246.8 vs 285.7 us for the bf16 forward + backward).  fp32: by reference,
+// which lets the compiler schedule four 32-bit loads; that form measured faster for fp32
+// (backward 245 vs 277 us at 16384 x 8192), where the kernel is HBM-bound anyway.
+template <typename T>
+__device__ __forceinline__ decltype(auto) stage_vec(const unsigned char* p) {
+  if constexpr (sizeof(T) == 4) {
+    return (*reinterpret_cast<const Pack<T, 4>*>(p));
+  } else {
+    return ld_smem16<T>(p);
+  }
+}
+
 // tiles of CTA b: t = b + i * gridDim.x  (evaluated once per CTA)
 __device__ __forceinline__ int my_tile_count(int64_t n_tiles) {
   return (int64_t)blockIdx.x < n_tiles ? (int)((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
@@ -199,7 +212,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<TI, VEC>(ld_smem16<TI>(st + k * k_off), f[k]);
+        unpack<TI, VEC>(stage_vec<TI>(st + k * k_off), f[k]);
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) f[k][e] = 0.f;
@@ -211,7 +224,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       for (int k = 0; k < K; ++k) {
         if (FULL || (row_ok && vok[k])) {
           float r[VEC];
-          unpack<TI, VEC>(ld_smem16<TI>(st + g.second_off + k * k_off), r);
+          unpack<TI, VEC>(stage_vec<TI>(st + g.second_off + k * k_off), r);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) f[k][e] += r[e];
           // the sum is rounded to the I/O type first: that value is normalized and stored
@@ -433,8 +446,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<T, VEC>(ld_smem16<T>(st + k * k_off), dyf[k]);
-        unpack<T, VEC>(ld_smem16<T>(st + g.second_off + k * k_off), xh[k]);
+        unpack<T, VEC>(stage_vec<T>(st + k * k_off), dyf[k]);
+        unpack<T, VEC>(stage_vec<T>(st + g.second_off + k * k_off), xh[k]);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) xh[k][e] = (xh[k][e] - mean) * rstd;
       } else {
@@ -619,8 +632,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe2_kernel(const BwdParams p, 
       float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        unpack<T, VEC>(ld_smem16<T>(st + rr * rr_off + k * k_off), dyf[rr][k]);
-        unpack<T, VEC>(ld_smem16<T>(st + g.second_off + rr * rr_off + k * k_off), xh[rr][k]);
+        unpack<T, VEC>(stage_vec<T>(st + rr * rr_off + k * k_off), dyf[rr][k]);
+        unpack<T, VEC>(stage_vec<T>(st + g.second_off + rr * rr_off + k * k_off), xh[rr][k]);
 #pragma unroll
         for (int e = 0; e < VEC; e += 2) {
           xh[rr][k][e] = (xh[rr][k][e] - mean[rr]) * rstd[rr];
