@@ -9,6 +9,11 @@
 //            Rows are walked from the last to the first so the rows phase 1 wrote most
 //            recently are still in L2.
 // There is no grid-wide wait anywhere.  The reference has no counterpart.
+//
+// Both kernels follow the register-resident forward (fln_forward.cu): the row lives in
+// registers as floats, statistics are the shifted two-pass form with sum reductions, 16-bit
+// values are widened / narrowed in pairs, fp8 codes are produced two at a time, and the FULL
+// instantiation carries no bounds checks.
 #include "fln_common.cuh"
 
 namespace fln {
@@ -37,9 +42,35 @@ struct Fp8MaxThreads {
   static constexpr int value = K <= 2 ? 1024 : 512;
 };
 
-template <typename TI, int VEC, int K, int KIND>
+// y (before quantization) of this thread's vectors, from the centred row and the statistics
+template <typename TI, int VEC>
+__device__ __forceinline__ void affine(float (&o)[VEC], const float (&f)[VEC], float rstd, const TI* gp,
+                                       const TI* bp, int64_t off) {
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) o[i] = f[i] * rstd;
+  if (gp != nullptr) {
+    float g[VEC];
+    unpack<TI, VEC>(ld_param<TI, VEC>(gp + off), g);
+    if (bp != nullptr) {
+      float b[VEC];
+      unpack<TI, VEC>(ld_param<TI, VEC>(bp + off), b);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = fmaf(o[i], g[i], b[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] *= g[i];
+    }
+  } else if (bp != nullptr) {
+    float b[VEC];
+    unpack<TI, VEC>(ld_param<TI, VEC>(bp + off), b);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] += b[i];
+  }
+}
+
+template <typename TI, int VEC, int K, int KIND, bool FULL>
 __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(const Fp8Params p) {
-  __shared__ float s_red[96];
+  __shared__ __align__(16) float s_red[2][32];
   __shared__ float s_max[32];
 
   const int tid = threadIdx.x;
@@ -48,19 +79,26 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
   const int row_in_cta = tid >> p.log2_tpr;
   const int rows_per_cta = blockDim.x >> p.log2_tpr;
   const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
-  const bool row_ok = row < p.rows;
-  const int64_t base = row * (int64_t)p.cols;
+  const bool row_ok = FULL ? true : row < p.rows;
+  const int64_t base = row_ok ? row * (int64_t)p.cols : 0;
+  const float inv_n = 1.0f / (float)p.cols;
   const TI* __restrict__ xr = reinterpret_cast<const TI*>(p.x) + base;
 
-  Pack<TI, VEC> raw[K];
+  float c = 0.f;  // shift for the LayerNorm statistics: element 0 of the (summed) row
+  if (KIND == FLN_LAYERNORM) {
+    c = Cvt<TI>::to_f(ld_param<TI, 1>(xr).e[0]);
+    if (p.res != nullptr)
+      c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(ld_param<TI, 1>(reinterpret_cast<const TI*>(p.res) + base).e[0])));
+  }
+  float f[K][VEC];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (row_ok && iv < p.nv) {
-      raw[k] = ld_stream<TI, VEC>(xr + (int64_t)iv * VEC);
+    if (FULL || (row_ok && iv < p.nv)) {
+      unpack<TI, VEC>(ld_stream<TI, VEC>(xr + (int64_t)iv * VEC), f[k]);
     } else {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) raw[k].e[i] = Cvt<TI>::from_f(0.f);
+      for (int i = 0; i < VEC; ++i) f[k][i] = 0.f;
     }
   }
   if (p.res != nullptr) {
@@ -69,60 +107,58 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int iv = lane_r + k * tpr;
-      if (row_ok && iv < p.nv) {
-        Pack<TI, VEC> r = ld_stream<TI, VEC>(rr + (int64_t)iv * VEC);
+      if (FULL || (row_ok && iv < p.nv)) {
+        float r[VEC];
+        unpack<TI, VEC>(ld_stream<TI, VEC>(rr + (int64_t)iv * VEC), r);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-          raw[k].e[i] = Cvt<TI>::from_f(Cvt<TI>::to_f(raw[k].e[i]) + Cvt<TI>::to_f(r.e[i]));
+        for (int i = 0; i < VEC; ++i) f[k][i] += r[i];
+        Pack<TI, VEC> q;
+        pack<TI, VEC>(f[k], q);
         // plain store: phase 2 wants to find these lines in L2
-        st_plain<TI, VEC>(sr + (int64_t)iv * VEC, raw[k]);
+        st_plain<TI, VEC>(sr + (int64_t)iv * VEC, q);
+        unpack<TI, VEC>(q, f[k]);
       }
     }
   }
 
-  float mean = 0.f, rstd;
+  float mean = 0.f;
   if (KIND == FLN_LAYERNORM) {
-    float lsum = 0.f, cnt = 0.f;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      const int iv = lane_r + k * tpr;
-      if (iv < p.nv) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) lsum += Cvt<TI>::to_f(raw[k].e[i]);
-        cnt += (float)VEC;
-      }
-    }
-    Wf w;
-    w.n = cnt;
-    w.mean = cnt > 0.f ? lsum / cnt : 0.f;
-    w.m2 = 0.f;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int iv = lane_r + k * tpr;
-      if (iv < p.nv) {
+      if (FULL || lane_r + k * tpr < p.nv) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          float d = Cvt<TI>::to_f(raw[k].e[i]) - w.mean;
-          w.m2 += d * d;
+          f[k][i] -= c;
+          a4[(k * VEC + i) & 3] += f[k][i];
         }
       }
     }
-    w = group_reduce_wf(w, tpr, s_red);
-    mean = w.mean;
-    rstd = 1.0f / sqrtf(w.m2 / (float)p.cols + p.eps);
-  } else {
-    float ss[1] = {0.f};
+    float a[1] = {(a4[0] + a4[1]) + (a4[2] + a4[3])};
+    rowsum_warp<1>(a, tpr, s_red[0]);
+    if (tpr > 32) __syncthreads();
+    rowsum_cta<1>(a, tpr, s_red[0]);
+    const float ms = a[0] * inv_n;
+    mean = c + ms;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      if (FULL || lane_r + k * tpr < p.nv) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float v = Cvt<TI>::to_f(raw[k].e[i]);
-        ss[0] += v * v;
+        for (int i = 0; i < VEC; ++i) f[k][i] -= ms;
       }
     }
-    group_reduce_sum<1>(ss, tpr, s_red);
-    rstd = 1.0f / sqrtf(ss[0] / (float)p.cols + p.eps);
   }
+  float q4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) q4[(k * VEC + i) & 3] = fmaf(f[k][i], f[k][i], q4[(k * VEC + i) & 3]);
+  }
+  float qs[1] = {(q4[0] + q4[1]) + (q4[2] + q4[3])};
+  rowsum_warp<1>(qs, tpr, s_red[1]);
+  if (tpr > 32) __syncthreads();
+  rowsum_cta<1>(qs, tpr, s_red[1]);
+  const float rstd = rsqrtf(qs[0] * inv_n + p.eps);
   if (row_ok && lane_r == 0) {
     if (KIND == FLN_LAYERNORM) p.mean[row] = mean;
     p.rstd[row] = rstd;
@@ -134,25 +170,15 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (row_ok && iv < p.nv) {
-      float v[VEC];
+    if (FULL || (row_ok && iv < p.nv)) {
+      float o[VEC];
+      affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
-      if (gp != nullptr) {
-        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
-      }
-      if (bp != nullptr) {
-        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
-      }
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(v[i]));  // fmaxf drops NaN
+      for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(o[i]));  // fmaxf drops NaN
     }
   }
   // CTA-wide max, then one atomic per CTA
+#pragma unroll
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
   const int lane = tid & 31, warp = tid >> 5;
   if (lane == 0) s_max[warp] = amax;
@@ -160,12 +186,26 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
   if (warp == 0) {
     const int nw = (blockDim.x + 31) >> 5;
     float m = lane < nw ? s_max[lane] : 0.f;
+#pragma unroll
     for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
     if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(m));
   }
 }
 
-template <typename TI, int VEC, int K, int KIND>
+// VEC saturating e4m3 codes from VEC floats, two per conversion instruction
+template <int VEC>
+__device__ __forceinline__ void pack_fp8(const float (&v)[VEC], Pack<unsigned char, VEC>& o) {
+  if constexpr (VEC >= 2) {
+    unsigned short* w = reinterpret_cast<unsigned short*>(&o);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j)
+      w[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * j], v[2 * j + 1]), __NV_SATFINITE, __NV_E4M3);
+  } else {
+    o.e[0] = (unsigned char)__nv_cvt_float_to_fp8(v[0], __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+template <typename TI, int VEC, int K, int KIND, bool FULL>
 __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(const Fp8Params p) {
   const int tid = threadIdx.x;
   const int tpr = p.tpr;
@@ -174,22 +214,21 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(con
   const int rows_per_cta = blockDim.x >> p.log2_tpr;
   // last rows first
   const int64_t row = p.rows - 1 - ((int64_t)blockIdx.x * rows_per_cta + row_in_cta);
-  if (row < 0) return;
+  if (!FULL && row < 0) return;
   const int64_t base = row * (int64_t)p.cols;
-  const TI* __restrict__ sr =
-      reinterpret_cast<const TI*>(p.res != nullptr ? p.sum_out : p.x) + base;
+  const TI* __restrict__ sr = reinterpret_cast<const TI*>(p.res != nullptr ? p.sum_out : p.x) + base;
 
-  Pack<TI, VEC> raw[K];
+  float f[K][VEC];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (iv < p.nv) raw[k] = ld_stream<TI, VEC>(sr + (int64_t)iv * VEC);
+    if (FULL || iv < p.nv) unpack<TI, VEC>(ld_stream<TI, VEC>(sr + (int64_t)iv * VEC), f[k]);
   }
   const float am = *p.amax;
   const float scale = am > 0.f ? 448.0f / am : 1.0f;
   if (blockIdx.x == 0 && tid == 0) *p.scale = scale;
-  const float mean = KIND == FLN_LAYERNORM ? p.mean[row] : 0.f;
-  const float rstd = p.rstd[row];
+  const float mean = KIND == FLN_LAYERNORM ? __ldg(p.mean + row) : 0.f;
+  const float rstd = __ldg(p.rstd + row);
 
   const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
   const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
@@ -197,43 +236,42 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(con
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (iv < p.nv) {
-      float v[VEC];
+    if (FULL || iv < p.nv) {
+      float o[VEC];
+      if (KIND == FLN_LAYERNORM) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = (Cvt<TI>::to_f(raw[k].e[i]) - mean) * rstd;
-      if (gp != nullptr) {
-        Pack<TI, VEC> g = ld_param<TI, VEC>(gp + (int64_t)iv * VEC);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] *= Cvt<TI>::to_f(g.e[i]);
+        for (int i = 0; i < VEC; ++i) f[k][i] -= mean;
       }
-      if (bp != nullptr) {
-        Pack<TI, VEC> b = ld_param<TI, VEC>(bp + (int64_t)iv * VEC);
+      affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] += Cvt<TI>::to_f(b.e[i]);
-      }
-      Pack<unsigned char, VEC> o;
-#pragma unroll
-      for (int i = 0; i < VEC; ++i)
-        o.e[i] = (unsigned char)__nv_cvt_float_to_fp8(v[i] * scale, __NV_SATFINITE, __NV_E4M3);
-      st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, o);
+      for (int i = 0; i < VEC; ++i) o[i] *= scale;
+      Pack<unsigned char, VEC> out;
+      pack_fp8<VEC>(o, out);
+      st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
     }
   }
 }
 
 template <typename TI, int KIND>
 static int run_fp8(Fp8Params p, cudaStream_t st) {
-  constexpr int FULL = 16 / sizeof(TI);
+  constexpr int VFULL = 16 / sizeof(TI);
   Plan pl = make_plan(false, p.rows, p.cols, (int)sizeof(TI), true);
-  if (pl.generic || pl.vec != FULL) return FLN_ERR_UNSUPPORTED;
+  if (pl.generic || pl.vec != VFULL) return FLN_ERR_UNSUPPORTED;
   p.tpr = pl.tpr;
   p.log2_tpr = pl.log2_tpr;
-  p.nv = p.cols / FULL;
+  p.nv = p.cols / VFULL;
   const unsigned grid = (unsigned)((p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta);
+  const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
   if (cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
-#define FLN_FP8_CASE(KK)                                                       \
-  case KK:                                                                     \
-    norm_amax_kernel<TI, FULL, KK, KIND><<<grid, pl.threads, 0, st>>>(p);      \
-    norm_quant_kernel<TI, FULL, KK, KIND><<<grid, pl.threads, 0, st>>>(p);     \
+#define FLN_FP8_CASE(KK)                                                               \
+  case KK:                                                                             \
+    if (full) {                                                                        \
+      norm_amax_kernel<TI, VFULL, KK, KIND, true><<<grid, pl.threads, 0, st>>>(p);     \
+      norm_quant_kernel<TI, VFULL, KK, KIND, true><<<grid, pl.threads, 0, st>>>(p);    \
+    } else {                                                                           \
+      norm_amax_kernel<TI, VFULL, KK, KIND, false><<<grid, pl.threads, 0, st>>>(p);    \
+      norm_quant_kernel<TI, VFULL, KK, KIND, false><<<grid, pl.threads, 0, st>>>(p);   \
+    }                                                                                  \
     break;
   switch (pl.K) {
     FLN_FP8_CASE(1)
