@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-sample-rows", type=int, default=2048)
+    ap.add_argument("--sm-reserve", type=int, default=-1,
+                    help="SMs the persistent kernels leave free (default: 0 on one GPU, 2 when an all-reduce overlaps)")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-small", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -220,6 +222,11 @@ def run_ours(args):
     from fused_layernorm import _capi as capi
     from fused_layernorm.hostio import HostLayerNormFwdBwd
 
+    # With N > 1 NCCL's all-reduce kernel runs beside the next forward; the persistent grids
+    # leave a few SMs free for it (see fln_set_sm_reserve).
+    sm_reserve = args.sm_reserve if args.sm_reserve >= 0 else (2 if world > 1 else 0)
+    capi.lib().fln_set_sm_reserve(sm_reserve)
+
     rows, cols, dt = args.rows, args.cols, torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(20245 + rank)
     x = torch.randn(rows, cols, device="cuda", generator=g).to(dt)
@@ -352,7 +359,8 @@ def run_ours(args):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"layernorm fwd+bwd {rows}x{cols} bf16 per GPU", "rows_per_gpu": rows, "cols": cols,
                    "total_rows": rows * world, "eps": 1e-5, "l2": "every tensor (256 MiB) is larger than the 126 MB L2",
-                   "collective": "ncclAllReduce fp32[2*cols] per step" if world > 1 else "none"},
+                   "collective": "ncclAllReduce fp32[2*cols] per step" if world > 1 else "none",
+                   "sm_reserve": sm_reserve},
         "rows_per_s": rows * world / (ms_per_step * 1e-3),
         "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
         "frac_of_" + peak_src: value / world / peak,

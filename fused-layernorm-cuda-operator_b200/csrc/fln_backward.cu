@@ -323,7 +323,7 @@ static BwdLaunch plan_bwd(int64_t rows, int cols, bool aligned) {
     return L;
   }
   L.row_groups = (rows + L.pl.rows_per_cta - 1) / L.pl.rows_per_cta;
-  int64_t cap = (int64_t)sm_count() * occupancy_dispatch<T, KIND>(L.pl);
+  int64_t cap = (int64_t)usable_sms() * occupancy_dispatch<T, KIND>(L.pl);
   L.grid = L.row_groups < cap ? L.row_groups : cap;
   L.P = L.grid * L.pl.rows_per_cta;
   return L;

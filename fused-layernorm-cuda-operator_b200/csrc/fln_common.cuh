@@ -457,7 +457,8 @@ struct Plan {
   int rows_per_cta;
 };
 
-int sm_count();  // of the current device, cached
+int sm_count();    // of the current device, cached
+int usable_sms();  // sm_count() minus the SMs persistent grids are asked to leave free
 Plan make_plan(bool backward, int64_t rows, int cols, int elem_bytes, bool aligned16);
 void plan_override(int* K, int* tpr);
 

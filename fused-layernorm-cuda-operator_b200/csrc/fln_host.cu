@@ -37,6 +37,13 @@ int sm_count() {
   return v;
 }
 
+static std::atomic<int> g_sm_reserve{0};
+
+int usable_sms() {
+  const int n = sm_count() - g_sm_reserve.load(std::memory_order_relaxed);
+  return n > 1 ? n : 1;
+}
+
 void plan_override(int* K, int* tpr) {
   *K = g_force_k.load(std::memory_order_relaxed);
   *tpr = g_force_tpr.load(std::memory_order_relaxed);
@@ -141,6 +148,8 @@ extern "C" void fln_set_plan_override(int vecs_per_thread, int threads_per_row) 
   g_force_k.store(vecs_per_thread, std::memory_order_relaxed);
   g_force_tpr.store(threads_per_row, std::memory_order_relaxed);
 }
+
+extern "C" void fln_set_sm_reserve(int sms) { g_sm_reserve.store(sms < 0 ? 0 : sms, std::memory_order_relaxed); }
 
 extern "C" const char* fln_status_string(int status) {
   switch (status) {

@@ -798,7 +798,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
   const int64_t n_tiles = (rows + R - 1) / R;
   const int by_smem = (int)((227 * 1024) / P.smem), by_threads = 2048 / threads;
   const int per_sm = by_smem < by_threads ? by_smem : by_threads;
-  const int64_t cap = (int64_t)sm_count() * (per_sm < 1 ? 1 : per_sm);
+  const int64_t cap = (int64_t)usable_sms() * (per_sm < 1 ? 1 : per_sm);
   P.grid = (int)(n_tiles < cap ? n_tiles : cap);
   return P;
 }

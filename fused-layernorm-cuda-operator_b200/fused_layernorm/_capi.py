@@ -28,7 +28,7 @@ SYMBOLS = [
     "fln_backward_workspace_bytes", "fln_layernorm_backward", "fln_norm_backward", "fln_cast_from_f32",
     "fln_graph_begin", "fln_graph_stream", "fln_graph_end", "fln_graph_launch", "fln_graph_destroy",
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
-    "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static",
+    "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -81,6 +81,8 @@ def lib() -> C.CDLL:
     L.fln_set_path_override.argtypes = [i32]
     L.fln_set_path_override.restype = None
     L.fln_device_status.restype = i32
+    L.fln_set_sm_reserve.argtypes = [i32]
+    L.fln_set_sm_reserve.restype = None
     L.fln_layernorm_backward_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, vp]
     _lib = L
     return L
