@@ -281,30 +281,45 @@ def run_ours(args):
     torch.cuda.synchronize()
 
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
-    # the barrier comes last, so every rank enters the timed region together
-    if dist:
-        dist.barrier()
-    torch.cuda.synchronize()
-    for i in range(K):
-        ev[i][0].record()
-        fwd()
-        ev[i][1].record()
-        bwd()
-        if world > 1 and i == K - 1:
-            finish_pending()
-        ev[i][2].record()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
+
+    def timed_pass(per_phase):
+        """K steps between a barrier + synchronize on both sides.  per_phase=False is the
+        timed region proper: two events, first launch to last.  per_phase=True repeats the
+        same K steps with an event after every phase, which gives the per-kernel launch
+        durations of the roofline but costs a few us per step (an event between two kernels
+        keeps the second from being staged behind the first), so it is kept out of `value`."""
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        # the barrier comes last, so every rank enters the timed region together
+        if dist:
+            dist.barrier()
         torch.cuda.synchronize()
+        for i in range(K):
+            if per_phase or i == 0:
+                ev[i][0].record()
+            fwd()
+            if per_phase:
+                ev[i][1].record()
+            bwd()
+            if world > 1 and i == K - 1:
+                finish_pending()
+            if per_phase or i == K - 1:
+                ev[i][2].record()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+            torch.cuda.synchronize()
+        return ev
+
+    ev = timed_pass(False)
     total_ms = ev[0][0].elapsed_time(ev[K - 1][2])
+    ev = timed_pass(True)
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    instrumented_ms = ev[0][0].elapsed_time(ev[K - 1][2]) / K
     clocks = sampler.stop() if rank == 0 else None
     if dist:
         t = torch.tensor([total_ms, fwd_ms, bwd_ms], device="cuda")
@@ -367,9 +382,11 @@ def run_ours(args):
         "roofline": {"kernel": "norm_bwd_pipe_kernel (+ colreduce_kernel, < 2 % of the time)", "bound": "hbm", "achieved": bwd_gbs,
                      "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch
-                     # (profiles/norm_bwd_pipe_kernel_16384x8192_bf16.md); only for the default workload
+                     # (profiles/layernorm_fwd_bwd_16384x8192_bf16.md); only for the default workload
                      "traffic": 769.4e6 if (rows, cols) == (16384, 8192) else None, "peak_source": peak_src,
-                     "algorithmic_bytes": bwd_b, "avg_ms": bwd_ms},
+                     "algorithmic_bytes": bwd_b, "avg_ms": bwd_ms,
+                     "timing": "CUDA events around every launch in a second pass of the same K steps "
+                               f"({instrumented_ms:.4f} ms/step with those events in the stream)"},
         "roofline_forward": {"kernel": "norm_fwd_pipe_kernel", "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
                              "unit": "GB/s", "frac": fwd_gbs / peak, "algorithmic_bytes": fwd_b, "avg_ms": fwd_ms},
         "clocks": clocks, "gpu_launches": K * launches_per_step,

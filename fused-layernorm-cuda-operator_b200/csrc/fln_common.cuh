@@ -151,17 +151,42 @@ __device__ __forceinline__ void pack(const float (&f)[VEC], Pack<T, VEC>& p) {
 }
 
 // Sum over the `tpr` threads that own a row, in two halves around the caller's CTA
-// barrier.  *_warp: butterfly inside the warp (all lanes of the group end up equal) and,
-// for groups of several warps, lane 0 parks the warp's value in shared memory.
-// *_cta: every thread adds the group's per-warp values in the same fixed order, so all of
-// them hold bit-identical totals without further shuffles.
+// barrier.  *_warp: butterfly inside the warp and, for groups of several warps, the warp's
+// value is parked in shared memory.  *_cta: every thread of the group combines the per-warp
+// values in the same fixed order, so all of them hold bit-identical totals.
+//
+// A pair of sums (NV == 2) is reduced "transposed": after one exchange across the half-warps
+// the lower 16 lanes carry sum 0 and the upper 16 lanes sum 1, so the remaining four butterfly
+// steps move one register instead of two (12 instead of 20 shuffle + add slots per row, and
+// these kernels are bound by instruction issue).  x + y == y + x bit for bit, so every lane
+// still ends with the same value as the plain butterfly would give.
+__device__ __forceinline__ void unzip_pair(float keep, bool hi, float (&v)[2]) {
+  const float other = __shfl_xor_sync(0xffffffffu, keep, 16);
+  v[0] = hi ? other : keep;
+  v[1] = hi ? keep : other;
+}
 template <int NV>
 __device__ __forceinline__ void rowsum_warp(float (&v)[NV], int tpr, float* smem) {
   if (tpr >= 32) {  // the usual case, fully unrolled
+    if constexpr (NV == 2) {
+      const int lane = threadIdx.x & 31;
+      const bool hi = (lane & 16) != 0;
+      float keep = hi ? v[1] : v[0];
+      keep += __shfl_xor_sync(0xffffffffu, hi ? v[0] : v[1], 16);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
+      for (int off = 8; off > 0; off >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, off);
+      if (tpr > 32) {
+        if ((lane & 15) == 0) smem[(lane >> 4) * 32 + (threadIdx.x >> 5)] = keep;
+      } else {
+        unzip_pair(keep, hi, v);
+      }
+      return;
+    } else {
 #pragma unroll
-      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+      }
     }
   } else {
     for (int off = tpr >> 1; off > 0; off >>= 1) {
@@ -194,6 +219,24 @@ __device__ __forceinline__ void rowsum_cta(float (&v)[NV], int tpr, const float*
   if (tpr > 32) {
     const int wpr = tpr >> 5;
     const int gbase = (threadIdx.x >> 5) & ~(wpr - 1);  // wpr is a power of two
+    if constexpr (NV <= 2) {
+      // many warps per row: one shared-memory word per lane and a four-step butterfly
+      // (again transposed for a pair) instead of 8 - 16 adds per sum in every thread
+      if ((NV == 2 && wpr == 8) || wpr == 16) {
+        const int lane = threadIdx.x & 31;
+        const int idx = lane & 15;
+        const int which = NV == 2 ? lane >> 4 : 0;
+        float keep = idx < wpr ? smem[which * 32 + gbase + idx] : 0.f;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, off);
+        if constexpr (NV == 2) {
+          unzip_pair(keep, which != 0, v);
+        } else {
+          v[0] = keep;
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const float* s = smem + i * 32 + gbase;

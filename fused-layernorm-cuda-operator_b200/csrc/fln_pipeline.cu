@@ -40,6 +40,23 @@ struct PipeGeom {
   uint32_t stage_stride;  // bytes per stage
 };
 
+#ifdef FLN_CTA_TRACE
+// Debug builds only: per-CTA start / end time (ns) and SM id of the last pipelined launch.
+__device__ unsigned long long g_cta_trace[3][1024];
+__device__ __forceinline__ void cta_trace(int slot) {
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    unsigned long long t;
+    unsigned int sm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    g_cta_trace[slot][blockIdx.x] = t;
+    g_cta_trace[2][blockIdx.x] = sm;
+  }
+}
+#else
+__device__ __forceinline__ void cta_trace(int) {}
+#endif
+
 constexpr int kSmemHeader = 2048;  // mbarriers + reduction scratch in front of the stages
 constexpr uint32_t kWaitLimit = 1u << 24;
 
@@ -154,6 +171,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   const bool has_res = p.res != nullptr;
   const float inv_n = 1.0f / (float)p.cols;
   const float eps = p.eps;
+  cta_trace(0);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
@@ -352,6 +370,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       phase ^= 1u;
     }
   }
+  cta_trace(1);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -376,6 +395,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   const int S = g.S;
   const int my_tiles = my_tile_count((p.rows + g.R - 1) / g.R);
   const float inv_n = 1.0f / (float)p.cols;
+  cta_trace(0);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
@@ -440,6 +460,10 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     }
     const bool landed = mbar_wait_bounded(&full[s], phase);
     const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
+    // 16-bit inputs: xhat as ONE fma, x * rstd - mean * rstd.  The rounding of mean * rstd
+    // costs 2^-24 |mean| / std in xhat, and 16-bit data cannot hold |mean| / std beyond 2^11,
+    // so this stays three orders below the output's own rounding.  fp32 keeps (x - mean) * rstd.
+    const float nmr = -mean * rstd;
 
     float xh[K][VEC], dyf[K][VEC];
     float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
@@ -449,7 +473,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
         unpack<T, VEC>(stage_vec<T>(st + k * k_off), dyf[k]);
         unpack<T, VEC>(stage_vec<T>(st + g.second_off + k * k_off), xh[k]);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) xh[k][e] = (xh[k][e] - mean) * rstd;
+        for (int e = 0; e < VEC; ++e)
+          xh[k][e] = sizeof(T) == 2 ? fmaf(xh[k][e], rstd, nmr) : (xh[k][e] - mean) * rstd;
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
@@ -491,7 +516,12 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
         if (FULL || (row_ok && vok[k])) {
           float o[VEC];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o[e] = rstd * fmaf(xh[k][e], nc1, dyf[k][e] * gam[k][e] - c2);
+          for (int e = 0; e < VEC; ++e) {
+            // the product of two 16-bit values is exact in fp32, so the fma equals
+            // (dy * gamma) - c2 bit for bit there and saves the multiply
+            const float gc = sizeof(T) == 2 ? fmaf(dyf[k][e], gam[k][e], -c2) : dyf[k][e] * gam[k][e] - c2;
+            o[e] = rstd * fmaf(xh[k][e], nc1, gc);
+          }
           Pack<T, VEC> out;
           pack<T, VEC>(o, out);
           st_stream<T, VEC>(dxr + (int64_t)k * tpr * VEC, out);
@@ -530,6 +560,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
       }
     }
   }
+  cta_trace(1);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -946,6 +977,12 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
 using namespace fln;
 
 extern "C" void fln_set_path_override(int mode) { g_path_override.store(mode, std::memory_order_relaxed); }
+
+#ifdef FLN_CTA_TRACE
+extern "C" int fln_debug_cta_trace(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, fln::g_cta_trace, sizeof(unsigned long long) * 3 * 1024);
+}
+#endif
 
 extern "C" int fln_device_status(void) {
   int v = 0;
