@@ -447,13 +447,23 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
       if (workspace == nullptr || workspace_bytes < need || !is_aligned16(workspace))
         return FLN_ERR_WORKSPACE;
       p.partials = reinterpret_cast<float*>(workspace);
+      // a workspace of the full advertised size has one more 16-byte slot behind the
+      // partial rows: the word the fused column reduce synchronises on
+      const size_t sync_off = (need + 15) & ~(size_t)15;
+      if (workspace_bytes >= sync_off + 16) {
+        p.sync = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(workspace) + sync_off);
+        p.dgb_f32 = dgb_f32;
+        p.dgamma = dgamma;
+        p.dbeta = dbeta;
+      }
     } else {
       p.partials = nullptr;
     }
-    const int rc = launch_bwd_pipeline(KIND, dt, p, st);
+    bool reduced = false;
+    const int rc = launch_bwd_pipeline(KIND, dt, p, st, &reduced);
     if (rc != FLN_PIPE_NOT_APPLICABLE) {
       if (rc != FLN_OK) return rc;
-      if (want_params) {
+      if (want_params && !reduced) {
         const int ncols = NR * p.cols;
         launch_colreduce<T>(p.partials, (int)pipeP, ncols, p.cols, dgb_f32, reinterpret_cast<T*>(dgamma),
                             reinterpret_cast<T*>(dbeta), st);
@@ -513,7 +523,8 @@ static size_t ws_bytes_typed(int64_t rows, int cols) {
   const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
   const int64_t pipeP = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols);
   if (pipeP > P) P = pipeP;
-  return (size_t)P * 2 * cols * sizeof(float);
+  // + one 16-byte slot for the grid barrier of the fused column reduce
+  return (((size_t)P * 2 * cols * sizeof(float) + 15) & ~(size_t)15) + 16;
 }
 
 }  // namespace fln
@@ -572,6 +583,11 @@ extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const 
   p.nv = 0;
   p.tpr = 0;
   p.log2_tpr = 0;
+  p.sync = nullptr;
+  p.token = 0;
+  p.dgb_f32 = nullptr;
+  p.dgamma = nullptr;
+  p.dbeta = nullptr;
   const bool aligned = is_aligned16(dy) && is_aligned16(x) && is_aligned16(gamma) &&
                        is_aligned16(dres_in) && is_aligned16(dx);
 #define FLN_RUN(T)                                                                         \

@@ -476,6 +476,16 @@ struct BwdParams {
   int nv;
   int tpr;
   int log2_tpr;
+  // Pipelined backward only: when `sync` is set the launch is cooperative, the grid meets at
+  // a barrier once the partial rows are written, and every CTA sums a slab of columns, so
+  // no second kernel is needed.  `sync` is one 8-byte word of the caller's workspace whose
+  // contents may be anything; `token` (never 0, different for every launch that is not a
+  // replay) lets the first arrival recognise and overwrite stale contents.
+  unsigned long long* sync;
+  unsigned long long token;
+  float* dgb_f32;
+  void* dgamma;
+  void* dbeta;
 };
 
 // Pipelined (bulk-async staged, persistent) variants, fln_pipeline.cu.  They return
@@ -483,7 +493,9 @@ struct BwdParams {
 constexpr int FLN_PIPE_NOT_APPLICABLE = -1;
 int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p,
                         cudaStream_t st);
-int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st);
+// *reduced tells whether dgamma / dbeta / dgb_f32 were produced by the launch itself (fused
+// column reduce); otherwise the caller reduces p.partials.
+int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);
 // partial rows the pipelined backward writes for this shape (0 = not applicable)
 int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols);
 

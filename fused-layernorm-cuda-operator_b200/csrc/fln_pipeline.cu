@@ -42,7 +42,7 @@ struct PipeGeom {
 
 #ifdef FLN_CTA_TRACE
 // Debug builds only: per-CTA start / end time (ns) and SM id of the last pipelined launch.
-__device__ unsigned long long g_cta_trace[3][1024];
+__device__ unsigned long long g_cta_trace[5][1024];
 __device__ __forceinline__ void cta_trace(int slot) {
   if (threadIdx.x == 0 && blockIdx.x < 1024) {
     unsigned long long t;
@@ -139,6 +139,41 @@ __device__ __forceinline__ void pipeline_abort(uint64_t* full, int S, int s, uin
       }
     }
   }
+}
+
+// ----------------------------------------------------------------------------------------
+// Grid barrier of a cooperative launch on one 64-bit word of caller memory with undefined
+// initial contents:  [63:24] token of the launch | [23:12] CTAs departed | [11:0] CTAs arrived.
+// The first CTA to look finds a foreign token and starts the count afresh; the last CTA to
+// depart writes 0 (no token is 0), so a graph replay with the same token starts clean as well.
+// Called by ONE thread per CTA, after a CTA barrier that follows the CTA's global writes.
+// The wait is bounded like every other wait here.
+// ----------------------------------------------------------------------------------------
+constexpr uint32_t kGridWaitLimit = 1u << 21;  // polls, >= 64 ns apart
+
+// At kernel start, one thread per CTA: make sure the word carries this launch's token.  One
+// compare-and-swap at most and no retry: if it fails, another CTA has initialised the word
+// (or has already counted itself in), which is all that is needed.  (Counting arrivals with a
+// compare-and-swap loop instead costs a round trip to L2 per CTA *in sequence*: 53 us for 148.)
+__device__ __forceinline__ void grid_barrier_init(unsigned long long* w, unsigned long long token) {
+  const unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(w);
+  if ((old >> 24) != token) atomicCAS(w, old, token << 24);
+}
+__device__ __forceinline__ bool grid_arrive_and_wait(unsigned long long* w, unsigned long long token,
+                                                     unsigned int grid) {
+  __threadfence();
+  atomicAdd(w, 1ull);
+  for (uint32_t it = 0; it < kGridWaitLimit; ++it) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(w) : "memory");
+    if ((v >> 24) == token && (unsigned int)(v & 0xfffull) == grid) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void grid_depart(unsigned long long* w, unsigned int grid) {
+  const unsigned long long old = atomicAdd(w, 1ull << 12);
+  if ((unsigned int)((old >> 12) & 0xfffull) == grid - 1) atomicExch(w, 0ull);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -374,12 +409,87 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 }
 
 // ----------------------------------------------------------------------------------------
+// Fused column reduce, the tail of the pipelined backward.  The partial rows were written a
+// moment ago and sit in L2; after the grid barrier CTA q sums columns [128 q, 128 q + 128)
+// over all partial rows: a warp per 512-byte row segment, the rows split over the 16 warps,
+// every thread's (up to ten) 16-byte loads issued before its first add, then the 16 warps
+// combined through the now idle stage memory `sb` (16 x 128 floats).  The order of the adds
+// is fixed, so the sums are reproducible.  Kept out of line so that the register allocation
+// of the streaming loop does not depend on it.
+// ----------------------------------------------------------------------------------------
+struct ReduceArgs {
+  const float* partials;
+  unsigned long long* sync;
+  unsigned long long token;
+  float* dgb_f32;
+  void* dgamma;
+  void* dbeta;
+  int cols;
+  int P;  // partial rows
+};
+template <typename T, int NR>
+__device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb) {
+  const int tid = threadIdx.x;
+  __syncthreads();
+  bool met = true;
+  if (tid == 0) met = grid_arrive_and_wait(p.sync, p.token, gridDim.x);
+  if (!__syncthreads_and(met ? 1 : 0)) {
+    if (tid == 0) atomicExch(&g_device_status, 2);
+    return;
+  }
+  cta_trace(3);
+  const int ncols = NR * p.cols;
+  const int n4 = ncols >> 2;
+  const int P = p.P;
+  const int cl = tid & 31, rg = tid >> 5;
+  for (int q = blockIdx.x; q * 32 < n4; q += gridDim.x) {
+    const int c4 = q * 32 + cl;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c4 < n4 && rg < 16) {
+      const float4* __restrict__ src = reinterpret_cast<const float4*>(p.partials) + c4;
+      for (int base = rg; base < P; base += 160) {
+        float4 v[10];
+#pragma unroll
+        for (int j = 0; j < 10; ++j) {
+          const int idx = base + j * 16;
+          v[j] = idx < P ? __ldcg(src + (int64_t)idx * n4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 10; ++j) {
+          acc.x += v[j].x;
+          acc.y += v[j].y;
+          acc.z += v[j].z;
+          acc.w += v[j].w;
+        }
+      }
+    }
+    if (rg < 16) *reinterpret_cast<float4*>(sb + rg * 128 + cl * 4) = acc;
+    __syncthreads();
+    const int c = q * 128 + tid;
+    if (tid < 128 && c < ncols) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) t += sb[i * 128 + tid];
+      if (p.dgb_f32 != nullptr) p.dgb_f32[c] = t;
+      if (c < p.cols) {
+        if (p.dgamma != nullptr) reinterpret_cast<T*>(p.dgamma)[c] = Cvt<T>::from_f(t);
+      } else {
+        if (p.dbeta != nullptr) reinterpret_cast<T*>(p.dbeta)[c - p.cols] = Cvt<T>::from_f(t);
+      }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) grid_depart(p.sync, gridDim.x);
+  cta_trace(4);
+}
+
+// ----------------------------------------------------------------------------------------
 // backward (stage 1: dx and per-CTA partial sums of dgamma / dbeta)
 //
 // Per element: two widening shifts, (x - mean) * rstd, g = dy * gamma, two running sums,
 // then dx = rstd * ((g - c2) - xhat * c1) and the two column accumulators.
 // ----------------------------------------------------------------------------------------
-template <typename T, int K, int KIND, bool FULL>
+template <typename T, int K, int KIND, bool FULL, bool FUSE>
 __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, const PipeGeom g) {
   constexpr int VEC = 16 / sizeof(T);
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
@@ -401,6 +511,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
+  if (FUSE && tid == 32) grid_barrier_init(p.sync, p.token);
   __syncthreads();
 
   auto issue = [&](int i, int s) {
@@ -561,6 +672,19 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     }
   }
   cta_trace(1);
+
+  if (FUSE) {
+    ReduceArgs a;
+    a.partials = p.partials;
+    a.sync = p.sync;
+    a.token = p.token;
+    a.dgb_f32 = p.dgb_f32;
+    a.dgamma = p.dgamma;
+    a.dbeta = p.dbeta;
+    a.cols = p.cols;
+    a.P = (int)gridDim.x * g.R;
+    fused_column_reduce<T, NR>(a, reinterpret_cast<float*>(stages));
+  }
 }
 
 // ----------------------------------------------------------------------------------------
@@ -744,7 +868,9 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe2_kernel(const BwdParams p, 
 // ----------------------------------------------------------------------------------------
 // host: geometry and dispatch
 // ----------------------------------------------------------------------------------------
-static std::atomic<int> g_path_override{0};  // 0 auto, 1 register kernels only, 2 pipeline whenever it fits
+// 0 auto, 1 register kernels only, 2 pipeline whenever it fits, 3 as 2 with the column reduce
+// as a second kernel, 4 as 2 with the two-rows-per-barrier backward
+static std::atomic<int> g_path_override{0};
 
 struct PipePlan {
   bool ok;
@@ -837,7 +963,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
 static bool pipeline_wanted(const PipePlan& P, int64_t rows) {
   const int ov = g_path_override.load(std::memory_order_relaxed);
   if (!P.ok || ov == 1) return false;
-  if (ov == 2 || ov == 4) return true;
+  if (ov == 2 || ov == 3 || ov == 4) return true;
   // worth it once every CTA streams several tiles
   const int64_t n_tiles = (rows + P.g.R - 1) / P.g.R;
   return n_tiles >= 4LL * P.grid || n_tiles >= 8LL * sm_count();
@@ -910,9 +1036,30 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
 #define FLN_LAUNCH(KK, FF)                                                                   \
   {                                                                                          \
-    auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF>;                \
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                             \
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                         \
+    if (p.sync != nullptr) {                                                                 \
+      /* the grid barrier needs every CTA resident: cooperative launch */                   \
+      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, true>;        \
+      if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                           \
+      cudaLaunchConfig_t cfg;                                                                \
+      memset(&cfg, 0, sizeof(cfg));                                                          \
+      cfg.gridDim = dim3((unsigned)P.grid);                                                  \
+      cfg.blockDim = dim3((unsigned)P.threads);                                              \
+      cfg.dynamicSmemBytes = P.smem;                                                         \
+      cfg.stream = st;                                                                       \
+      cudaLaunchAttribute attr;                                                              \
+      attr.id = cudaLaunchAttributeCooperative;                                              \
+      attr.val.cooperative = 1;                                                              \
+      cfg.attrs = &attr;                                                                     \
+      cfg.numAttrs = 1;                                                                      \
+      if (cudaLaunchKernelEx(&cfg, kern, p, P.g) != cudaSuccess) {                           \
+        cudaGetLastError();                                                                  \
+        return FLN_ERR_LAUNCH;                                                               \
+      }                                                                                      \
+    } else {                                                                                 \
+      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, false>;       \
+      if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                           \
+      kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                       \
+    }                                                                                        \
   }
 #define FLN_LAUNCH2(KK)                                                                      \
   {                                                                                          \
@@ -958,17 +1105,59 @@ int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols) {
   return (int64_t)P.grid * (P.g.R / P.rpt);
 }
 
-int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t st) {
+static bool cooperative_launch_supported() {
+  static int cache[64];  // 0 unknown, 1 no, 2 yes
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (cache[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess) {
+      cudaGetLastError();
+      v = 0;
+    }
+    cache[dev] = v ? 2 : 1;
+  }
+  return cache[dev] == 2;
+}
+
+static unsigned long long next_launch_token() {
+  static std::atomic<unsigned long long> ctr{0x5bd1e995ull};
+  unsigned long long t;
+  do {
+    t = ctr.fetch_add(1, std::memory_order_relaxed) & ((1ull << 40) - 1);
+  } while (t == 0);
+  return t;
+}
+
+int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t st, bool* reduced) {
   const int es = dtype == FLN_F32 ? 4 : 2;
+  *reduced = false;
   PipePlan P = plan_bwd_pipeline(p0.rows, p0.cols, es);
   if (!pipeline_wanted(P, p0.rows) || p0.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
   BwdParams p = p0;
   p.nv = p.cols / (16 / es);
+  // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the
+  // one-row kernel, stage memory large enough for the 16 x 128 floats of the combine step.
+  const bool fuse = p.sync != nullptr && p.partials != nullptr && P.rpt == 1 && P.grid <= usable_sms() &&
+                    P.grid < 4096 && P.smem >= (size_t)kSmemHeader + 16 * 128 * sizeof(float) &&
+                    g_path_override.load(std::memory_order_relaxed) != 3 && cooperative_launch_supported();
+  if (fuse) {
+    p.token = next_launch_token();
+    *reduced = true;
+  } else {
+    p.sync = nullptr;
+  }
 #define FLN_RUN(T) \
   (kind == FLN_LAYERNORM ? bwd_pipe_k<T, FLN_LAYERNORM>(p, P, st) : bwd_pipe_k<T, FLN_RMSNORM>(p, P, st))
-  if (dtype == FLN_F32) return FLN_RUN(float);
-  if (dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
-  return FLN_RUN(__half);
+  int rc = dtype == FLN_F32 ? FLN_RUN(float) : (dtype == FLN_BF16 ? FLN_RUN(__nv_bfloat16) : FLN_RUN(__half));
+  if (rc == FLN_ERR_LAUNCH && fuse) {
+    // the cooperative launch was refused (the device is shared in a way that rules out a
+    // resident grid): run the plain launch and let the caller reduce the partial rows
+    p.sync = nullptr;
+    *reduced = false;
+    rc = dtype == FLN_F32 ? FLN_RUN(float) : (dtype == FLN_BF16 ? FLN_RUN(__nv_bfloat16) : FLN_RUN(__half));
+  }
+  return rc;
 #undef FLN_RUN
 }
 
@@ -980,7 +1169,7 @@ extern "C" void fln_set_path_override(int mode) { g_path_override.store(mode, st
 
 #ifdef FLN_CTA_TRACE
 extern "C" int fln_debug_cta_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, fln::g_cta_trace, sizeof(unsigned long long) * 3 * 1024);
+  return (int)cudaMemcpyFromSymbol(host_out, fln::g_cta_trace, sizeof(unsigned long long) * 5 * 1024);
 }
 #endif
 
