@@ -10,6 +10,13 @@
 //            recently are still in L2.
 // There is no grid-wide wait anywhere.  The reference has no counterpart.
 //
+// Two one-pass forms avoid the second read of s (7 instead of 9 bytes per element):
+//   delayed scaling  the caller supplies the scale (typically 448 / amax of the previous
+//                    step); the kernel quantizes with it and reports this call's amax;
+//   per-row scaling  every row gets its own scale 448 / max|y_row|, known once the row is
+//                    in registers, and the scales are returned as an fp32 vector.
+// Both are norm_amax_kernel with QMODE 1 / 2: same loads, same statistics, then the codes.
+//
 // Both kernels follow the register-resident forward (fln_forward.cu): the row lives in
 // registers as floats, statistics are the shifted two-pass form with sum reductions, 16-bit
 // values are widened / narrowed in pairs, fp8 codes are produced two at a time, and the FULL
@@ -29,6 +36,8 @@ struct Fp8Params {
   float* rstd;
   float* amax;
   float* scale;
+  const float* scale_in;  // QMODE 1: one fp32, read by every CTA
+  float* row_scale;       // QMODE 2: [rows] fp32, written
   int64_t rows;
   int cols;
   int nv;
@@ -68,10 +77,60 @@ __device__ __forceinline__ void affine(float (&o)[VEC], const float (&f)[VEC], f
   }
 }
 
-template <typename TI, int VEC, int K, int KIND, bool FULL>
+// VEC saturating e4m3 codes from VEC floats, two per conversion instruction
+template <int VEC>
+__device__ __forceinline__ void pack_fp8(const float (&v)[VEC], Pack<unsigned char, VEC>& o) {
+  if constexpr (VEC >= 2) {
+    unsigned short* w = reinterpret_cast<unsigned short*>(&o);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j)
+      w[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * j], v[2 * j + 1]), __NV_SATFINITE, __NV_E4M3);
+  } else {
+    o.e[0] = (unsigned char)__nv_cvt_float_to_fp8(v[0], __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
+// CTA-wide max of a non-negative value, folded into *dst with one atomic per CTA
+// (non-negative floats order like their bit patterns).  Contains a CTA barrier.
+__device__ __forceinline__ void cta_max_to_global(float m, float* s_max, float* dst) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_max[warp] = m;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = lane < nw ? s_max[lane] : 0.f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, off));
+    if (lane == 0 && t > 0.f) atomicMax(reinterpret_cast<unsigned int*>(dst), __float_as_uint(t));
+  }
+}
+// max over the tpr threads that own a row; every one of them gets the result
+__device__ __forceinline__ float row_max(float m, int tpr, float* smem) {
+  if (tpr >= 32) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  } else {
+    for (int off = tpr >> 1; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  }
+  if (tpr > 32) {
+    const int warp = threadIdx.x >> 5, wpr = tpr >> 5;
+    if ((threadIdx.x & 31) == 0) smem[warp] = m;
+    __syncthreads();
+    const int gbase = warp & ~(wpr - 1);
+    m = smem[gbase];
+    for (int j = 1; j < wpr; ++j) m = fmaxf(m, smem[gbase + j]);
+  }
+  return m;
+}
+
+// QMODE 0: phase 1 of the two-launch form (amax only); 1: quantize with *scale_in; 2: per-row scale
+template <typename TI, int VEC, int K, int KIND, bool FULL, int QMODE>
 __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(const Fp8Params p) {
   __shared__ __align__(16) float s_red[2][32];
   __shared__ float s_max[32];
+  __shared__ float s_rmax[32];
 
   const int tid = threadIdx.x;
   const int tpr = p.tpr;
@@ -114,8 +173,12 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
         for (int i = 0; i < VEC; ++i) f[k][i] += r[i];
         Pack<TI, VEC> q;
         pack<TI, VEC>(f[k], q);
-        // plain store: phase 2 wants to find these lines in L2
-        st_plain<TI, VEC>(sr + (int64_t)iv * VEC, q);
+        // two-launch form: plain store, phase 2 wants to find these lines in L2
+        if (QMODE == 0) {
+          st_plain<TI, VEC>(sr + (int64_t)iv * VEC, q);
+        } else {
+          st_stream<TI, VEC>(sr + (int64_t)iv * VEC, q);
+        }
         unpack<TI, VEC>(q, f[k]);
       }
     }
@@ -160,13 +223,16 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
   rowsum_cta<1>(qs, tpr, s_red[1]);
   const float rstd = rsqrtf(qs[0] * inv_n + p.eps);
   if (row_ok && lane_r == 0) {
-    if (KIND == FLN_LAYERNORM) p.mean[row] = mean;
-    p.rstd[row] = rstd;
+    if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
+    if (p.rstd != nullptr) p.rstd[row] = rstd;
   }
 
   const TI* __restrict__ gp = reinterpret_cast<const TI*>(p.gamma);
   const TI* __restrict__ bp = reinterpret_cast<const TI*>(p.beta);
+  unsigned char* __restrict__ qr = reinterpret_cast<unsigned char*>(p.q) + base;
   float amax = 0.f;
+  float qscale = 1.f;
+  if (QMODE == 1) qscale = __ldg(p.scale_in);
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
@@ -175,34 +241,35 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
       affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) amax = fmaxf(amax, fabsf(o[i]));  // fmaxf drops NaN
+      if (QMODE == 1) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] *= qscale;
+        Pack<unsigned char, VEC> out;
+        pack_fp8<VEC>(o, out);
+        st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
+      }
     }
   }
-  // CTA-wide max, then one atomic per CTA
+  if (QMODE == 2) {
+    const float rmax = row_max(amax, tpr, s_rmax);
+    qscale = rmax > 0.f ? 448.0f / rmax : 1.0f;
+    if (row_ok && lane_r == 0) p.row_scale[row] = qscale;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  const int lane = tid & 31, warp = tid >> 5;
-  if (lane == 0) s_max[warp] = amax;
-  __syncthreads();
-  if (warp == 0) {
-    const int nw = (blockDim.x + 31) >> 5;
-    float m = lane < nw ? s_max[lane] : 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      if (FULL || (row_ok && iv < p.nv)) {
+        float o[VEC];
+        affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(m));
+        for (int i = 0; i < VEC; ++i) o[i] *= qscale;
+        Pack<unsigned char, VEC> out;
+        pack_fp8<VEC>(o, out);
+        st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
+      }
+    }
   }
-}
-
-// VEC saturating e4m3 codes from VEC floats, two per conversion instruction
-template <int VEC>
-__device__ __forceinline__ void pack_fp8(const float (&v)[VEC], Pack<unsigned char, VEC>& o) {
-  if constexpr (VEC >= 2) {
-    unsigned short* w = reinterpret_cast<unsigned short*>(&o);
-#pragma unroll
-    for (int j = 0; j < VEC / 2; ++j)
-      w[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * j], v[2 * j + 1]), __NV_SATFINITE, __NV_E4M3);
-  } else {
-    o.e[0] = (unsigned char)__nv_cvt_float_to_fp8(v[0], __NV_SATFINITE, __NV_E4M3);
-  }
+  // tensor-wide amax: always in the two-launch form, on request otherwise
+  if (QMODE == 0 || p.amax != nullptr) cta_max_to_global(amax, s_max, p.amax);
 }
 
 template <typename TI, int VEC, int K, int KIND, bool FULL>
@@ -253,7 +320,7 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(con
 }
 
 template <typename TI, int KIND>
-static int run_fp8(Fp8Params p, cudaStream_t st) {
+static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
   constexpr int VFULL = 16 / sizeof(TI);
   Plan pl = make_plan(false, p.rows, p.cols, (int)sizeof(TI), true);
   if (pl.generic || pl.vec != VFULL) return FLN_ERR_UNSUPPORTED;
@@ -262,16 +329,23 @@ static int run_fp8(Fp8Params p, cudaStream_t st) {
   p.nv = p.cols / VFULL;
   const unsigned grid = (unsigned)((p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta);
   const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
-  if (cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
-#define FLN_FP8_CASE(KK)                                                               \
-  case KK:                                                                             \
-    if (full) {                                                                        \
-      norm_amax_kernel<TI, VFULL, KK, KIND, true><<<grid, pl.threads, 0, st>>>(p);     \
-      norm_quant_kernel<TI, VFULL, KK, KIND, true><<<grid, pl.threads, 0, st>>>(p);    \
-    } else {                                                                           \
-      norm_amax_kernel<TI, VFULL, KK, KIND, false><<<grid, pl.threads, 0, st>>>(p);    \
-      norm_quant_kernel<TI, VFULL, KK, KIND, false><<<grid, pl.threads, 0, st>>>(p);   \
-    }                                                                                  \
+  if (p.amax != nullptr && cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+#define FLN_FP8_LAUNCH(KK, FF)                                                                  \
+  if (qmode == 0) {                                                                             \
+    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 0><<<grid, pl.threads, 0, st>>>(p);               \
+    norm_quant_kernel<TI, VFULL, KK, KIND, FF><<<grid, pl.threads, 0, st>>>(p);                 \
+  } else if (qmode == 1) {                                                                      \
+    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 1><<<grid, pl.threads, 0, st>>>(p);               \
+  } else {                                                                                      \
+    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 2><<<grid, pl.threads, 0, st>>>(p);               \
+  }
+#define FLN_FP8_CASE(KK)          \
+  case KK:                        \
+    if (full) {                   \
+      FLN_FP8_LAUNCH(KK, true)    \
+    } else {                      \
+      FLN_FP8_LAUNCH(KK, false)   \
+    }                             \
     break;
   switch (pl.K) {
     FLN_FP8_CASE(1)
@@ -282,6 +356,7 @@ static int run_fp8(Fp8Params p, cudaStream_t st) {
       return FLN_ERR_ARG;
   }
 #undef FLN_FP8_CASE
+#undef FLN_FP8_LAUNCH
   FLN_CHECK_LAUNCH();
   return FLN_OK;
 }
@@ -290,27 +365,30 @@ static int run_fp8(Fp8Params p, cudaStream_t st) {
 
 using namespace fln;
 
-extern "C" int fln_norm_forward_fp8(int kind, const void* x, const void* residual,
-                                    const void* gamma, const void* beta, void* q, void* sum_out,
-                                    float* mean, float* rstd, float* amax, float* scale,
-                                    int64_t rows, int64_t cols, int io_dtype, float eps,
-                                    void* stream) {
+static int fp8_entry(int qmode, int kind, const void* x, const void* residual, const void* gamma,
+                     const void* beta, void* q, void* sum_out, float* mean, float* rstd, float* amax,
+                     float* scale, const float* scale_in, float* row_scale, int64_t rows, int64_t cols,
+                     int io_dtype, float eps, void* stream) {
   if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
   if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
-  if (amax == nullptr || scale == nullptr) return FLN_ERR_NULL;
+  if (qmode == 0 && (amax == nullptr || scale == nullptr)) return FLN_ERR_NULL;
+  if (qmode == 1 && scale_in == nullptr) return FLN_ERR_NULL;
+  if (qmode == 2 && row_scale == nullptr) return FLN_ERR_NULL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (rows == 0) {
     // empty tensor: amax = 0, scale = 1
     const float one = 1.0f;
-    if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
-    if (cudaMemcpyAsync(scale, &one, sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
+    if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+    if (scale != nullptr &&
+        cudaMemcpyAsync(scale, &one, sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
       return FLN_ERR_LAUNCH;
     return FLN_OK;
   }
-  if (x == nullptr || q == nullptr || rstd == nullptr) return FLN_ERR_NULL;
+  if (x == nullptr || q == nullptr) return FLN_ERR_NULL;
+  if (qmode == 0 && rstd == nullptr) return FLN_ERR_NULL;  // phase 2 reads it
   if (residual != nullptr && sum_out == nullptr) return FLN_ERR_NULL;
-  if (kind == FLN_LAYERNORM && mean == nullptr) return FLN_ERR_NULL;
+  if (kind == FLN_LAYERNORM && qmode == 0 && mean == nullptr) return FLN_ERR_NULL;
   if (kind == FLN_RMSNORM && (beta != nullptr || mean != nullptr)) return FLN_ERR_ARG;
   const int es = io_dtype == FLN_F32 ? 4 : 2;
   if (cols % (16 / es) != 0) return FLN_ERR_UNSUPPORTED;
@@ -329,6 +407,8 @@ extern "C" int fln_norm_forward_fp8(int kind, const void* x, const void* residua
   p.rstd = rstd;
   p.amax = amax;
   p.scale = scale;
+  p.scale_in = scale_in;
+  p.row_scale = row_scale;
   p.rows = rows;
   p.cols = (int)cols;
   p.nv = 0;
@@ -336,9 +416,36 @@ extern "C" int fln_norm_forward_fp8(int kind, const void* x, const void* residua
   p.log2_tpr = 0;
   p.eps = eps;
 #define FLN_RUN(T) \
-  (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, st) : run_fp8<T, FLN_RMSNORM>(p, st))
+  (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, qmode, st) : run_fp8<T, FLN_RMSNORM>(p, qmode, st))
   if (io_dtype == FLN_F32) return FLN_RUN(float);
   if (io_dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
   return FLN_RUN(__half);
 #undef FLN_RUN
+}
+
+extern "C" int fln_norm_forward_fp8(int kind, const void* x, const void* residual,
+                                    const void* gamma, const void* beta, void* q, void* sum_out,
+                                    float* mean, float* rstd, float* amax, float* scale,
+                                    int64_t rows, int64_t cols, int io_dtype, float eps,
+                                    void* stream) {
+  return fp8_entry(0, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax, scale, nullptr, nullptr,
+                   rows, cols, io_dtype, eps, stream);
+}
+
+extern "C" int fln_norm_forward_fp8_delayed(int kind, const void* x, const void* residual,
+                                            const void* gamma, const void* beta, void* q, void* sum_out,
+                                            float* mean, float* rstd, const float* scale_in,
+                                            float* amax_out, int64_t rows, int64_t cols, int io_dtype,
+                                            float eps, void* stream) {
+  return fp8_entry(1, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, scale_in,
+                   nullptr, rows, cols, io_dtype, eps, stream);
+}
+
+extern "C" int fln_norm_forward_fp8_rowwise(int kind, const void* x, const void* residual,
+                                            const void* gamma, const void* beta, void* q, void* sum_out,
+                                            float* mean, float* rstd, float* row_scale, float* amax_out,
+                                            int64_t rows, int64_t cols, int io_dtype, float eps,
+                                            void* stream) {
+  return fp8_entry(2, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, nullptr,
+                   row_scale, rows, cols, io_dtype, eps, stream);
 }

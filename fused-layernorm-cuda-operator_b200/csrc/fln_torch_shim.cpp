@@ -200,6 +200,53 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> norm_fp8(int64_t kind, const 
   return {q, sum, amax_scale.slice(0, 1, 2), mean, rstd};
 }
 
+// One-pass fp8-e4m3 output: with `scale_in` (one fp32) the caller's scale is used (delayed
+// scaling), without it every row gets its own scale.  Returns (q, sum, row_scale, amax);
+// row_scale is empty in the delayed form, amax is max|y| of this call in both.
+std::tuple<Tensor, Tensor, Tensor, Tensor> norm_fp8_scaled(int64_t kind, const Tensor& input, const OptTensor& residual,
+                                                           const OptTensor& gamma, const OptTensor& beta,
+                                                           const OptTensor& scale_in, double epsilon) {
+  TORCH_CHECK(kind == FLN_LAYERNORM || kind == FLN_RMSNORM, "kind must be 0 (layernorm) or 1 (rmsnorm)");
+  Tensor x = check_matrix(input, "input");
+  const int dt = dtype_code(x, "norm_fp8_scaled");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor gk, bk, rk, sum, sk;
+  const void* g = param_ptr(gamma, x, "Gamma", gk);
+  const void* b = param_ptr(beta, x, "Beta", bk);
+  TORCH_CHECK(!(kind == FLN_RMSNORM && b != nullptr), "rmsnorm takes no beta");
+  const void* r = nullptr;
+  void* s = nullptr;
+  if (residual.has_value() && residual->defined()) {
+    rk = check_like(*residual, x, "residual");
+    r = rk.data_ptr();
+    sum = at::empty_like(x);
+    s = sum.data_ptr();
+  } else {
+    sum = at::empty({0}, x.options());
+  }
+  auto so = x.options().dtype(at::kFloat);
+  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor amax = at::empty({1}, so);
+  const bool delayed = scale_in.has_value() && scale_in->defined();
+  if (delayed) {
+    TORCH_CHECK(scale_in->is_cuda() && scale_in->device() == x.device() && scale_in->scalar_type() == at::kFloat &&
+                    scale_in->numel() == 1,
+                "scale must be one float32 on the input's device");
+    sk = scale_in->contiguous();
+    check_status(fln_norm_forward_fp8_delayed((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), s, nullptr, nullptr,
+                                              sk.data_ptr<float>(), amax.data_ptr<float>(), x.size(0), x.size(1), dt,
+                                              (float)epsilon, stream_of(x)),
+                 "norm_fp8_scaled");
+    return {q, sum, at::empty({0}, so), amax};
+  }
+  Tensor row_scale = at::empty({x.size(0)}, so);
+  check_status(fln_norm_forward_fp8_rowwise((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), s, nullptr, nullptr,
+                                            row_scale.data_ptr<float>(), amax.data_ptr<float>(), x.size(0), x.size(1),
+                                            dt, (float)epsilon, stream_of(x)),
+               "norm_fp8_scaled");
+  return {q, sum, row_scale, amax};
+}
+
 // ---------------------------------------------------------------------------------------
 // backward family
 // ---------------------------------------------------------------------------------------
@@ -320,6 +367,7 @@ TORCH_LIBRARY(fused_layernorm, m) {
   m.def("add_layernorm_fwd(Tensor input, Tensor residual, Tensor? gamma, Tensor? beta, float epsilon) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("add_rmsnorm_fwd(Tensor input, Tensor residual, Tensor? gamma, float epsilon) -> (Tensor, Tensor, Tensor)");
   m.def("norm_fp8(int kind, Tensor input, Tensor? residual, Tensor? gamma, Tensor? beta, float epsilon) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("norm_fp8_scaled(int kind, Tensor input, Tensor? residual, Tensor? gamma, Tensor? beta, Tensor? scale_in, float epsilon) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("layernorm_bwd(Tensor grad_output, Tensor input, Tensor mean, Tensor rstd, Tensor? gamma, Tensor? dres_in, bool need_dx, bool need_dgamma, bool need_dbeta) -> (Tensor, Tensor, Tensor)");
   m.def("rmsnorm_bwd(Tensor grad_output, Tensor input, Tensor rstd, Tensor? gamma, Tensor? dres_in, bool need_dx, bool need_dgamma) -> (Tensor, Tensor)");
   m.def("layernorm_bwd_f32(Tensor grad_output, Tensor input, Tensor mean, Tensor rstd, Tensor? gamma) -> (Tensor, Tensor)");
@@ -334,6 +382,7 @@ TORCH_LIBRARY_IMPL(fused_layernorm, CUDA, m) {
   m.impl("add_layernorm_fwd", &add_layernorm_fwd);
   m.impl("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.impl("norm_fp8", &norm_fp8);
+  m.impl("norm_fp8_scaled", &norm_fp8_scaled);
   m.impl("layernorm_bwd", &layernorm_bwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
   m.impl("layernorm_bwd_f32", &layernorm_bwd_f32);
@@ -416,6 +465,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       "(q fp8-e4m3, residual sum, scale = 448 / amax)", py::arg("input"), py::arg("residual") = py::none(),
       py::arg("gamma") = py::none(), py::arg("epsilon") = 1e-6);
+  m.def("norm_fp8_scaled", &norm_fp8_scaled, py::arg("kind"), py::arg("input"), py::arg("residual") = py::none(),
+        py::arg("gamma") = py::none(), py::arg("beta") = py::none(), py::arg("scale_in") = py::none(),
+        py::arg("epsilon") = 1e-5);
   m.def("norm_fp8", &norm_fp8, py::arg("kind"), py::arg("input"), py::arg("residual") = py::none(),
         py::arg("gamma") = py::none(), py::arg("beta") = py::none(), py::arg("epsilon") = 1e-5);
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("grad_output"), py::arg("input"), py::arg("mean"), py::arg("rstd"),

@@ -29,6 +29,7 @@ SYMBOLS = [
     "fln_graph_begin", "fln_graph_stream", "fln_graph_end", "fln_graph_launch", "fln_graph_destroy",
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
+    "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -61,6 +62,8 @@ def lib() -> C.CDLL:
     L.fln_layernorm_gelu_forward.argtypes = [vp, vp, vp, vp, i64, i64, i32, f32, i32, vp]
     L.fln_norm_forward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, f32, i32, vp]
     L.fln_norm_forward_fp8.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
+    L.fln_norm_forward_fp8_delayed.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
+    L.fln_norm_forward_fp8_rowwise.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_backward_workspace_bytes.restype = sz
     L.fln_backward_workspace_bytes.argtypes = [i64, i64, i32]
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
@@ -139,6 +142,26 @@ def norm_forward_fp8(kind, x, residual, gamma, beta, q, sum_out, mean, rstd, ama
     check(lib().fln_norm_forward_fp8(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q),
                                      ptr(sum_out), ptr(mean), ptr(rstd), ptr(amax), ptr(scale), rows, cols,
                                      dtype_code(x), eps, stream_handle(stream)), "fln_norm_forward_fp8")
+
+
+def norm_forward_fp8_delayed(kind, x, residual, gamma, beta, q, sum_out, mean, rstd, scale_in, amax_out, eps,
+                             stream=None):
+    """One launch: q = sat_e4m3(y * scale_in[0]); amax_out (optional) receives max|y| of this call."""
+    rows, cols = x.shape
+    check(lib().fln_norm_forward_fp8_delayed(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q),
+                                             ptr(sum_out), ptr(mean), ptr(rstd), ptr(scale_in), ptr(amax_out),
+                                             rows, cols, dtype_code(x), eps, stream_handle(stream)),
+          "fln_norm_forward_fp8_delayed")
+
+
+def norm_forward_fp8_rowwise(kind, x, residual, gamma, beta, q, sum_out, mean, rstd, row_scale, amax_out, eps,
+                             stream=None):
+    """One launch: row_scale[r] = 448 / max|y[r]|, q[r] = sat_e4m3(y[r] * row_scale[r])."""
+    rows, cols = x.shape
+    check(lib().fln_norm_forward_fp8_rowwise(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q),
+                                             ptr(sum_out), ptr(mean), ptr(rstd), ptr(row_scale), ptr(amax_out),
+                                             rows, cols, dtype_code(x), eps, stream_handle(stream)),
+          "fln_norm_forward_fp8_rowwise")
 
 
 def backward_workspace_bytes(rows, cols, dtype) -> int:

@@ -66,6 +66,14 @@ def _(kind, input, residual, gamma, beta, epsilon):
     return q, s, input.new_empty((1,), dtype=torch.float32), mean, _stat(input)
 
 
+@torch.library.register_fake("fused_layernorm::norm_fp8_scaled")
+def _(kind, input, residual, gamma, beta, scale_in, epsilon):
+    q = input.new_empty(input.shape, dtype=torch.float8_e4m3fn)
+    s = torch.empty_like(input, memory_format=torch.contiguous_format) if residual is not None else input.new_empty((0,))
+    row_scale = input.new_empty((0,), dtype=torch.float32) if scale_in is not None else _stat(input)
+    return q, s, row_scale, input.new_empty((1,), dtype=torch.float32)
+
+
 @torch.library.register_fake("fused_layernorm::layernorm_bwd")
 def _(grad_output, input, mean, rstd, gamma, dres_in, need_dx, need_dgamma, need_dbeta):
     cols = input.shape[1]

@@ -71,6 +71,33 @@ def fused_add_layer_norm_fp8(input: torch.Tensor, residual: Optional[torch.Tenso
     return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), scale
 
 
+def fused_add_norm_fp8_delayed(input: torch.Tensor, scale: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                               weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                               eps: float = 1e-6, kind: str = "rmsnorm"):
+    """(q, sum, amax) in ONE pass: q = norm(input + residual) * scale, saturated to float8_e4m3fn,
+    with a scale fixed beforehand (delayed scaling: usually 448 / amax of the previous step);
+    amax = max|y| of this call, for the next step's scale.  `scale` is one fp32 on the device.
+    7 instead of 9 bytes per element compared with fused_add_rms_norm_fp8.  Forward only."""
+    _require_cuda(input)
+    k = _ops.RMSNORM if kind == "rmsnorm" else _ops.LAYERNORM
+    q, s, _rs, amax = _t.norm_fp8_scaled(k, _flat(input), None if residual is None else _flat(residual), weight, bias,
+                                         scale, eps)
+    return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), amax
+
+
+def fused_add_norm_fp8_rowwise(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                               weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                               eps: float = 1e-6, kind: str = "rmsnorm"):
+    """(q, sum, row_scale) in ONE pass: every row is quantized with its own scale
+    448 / max|y[row]| (1 for an all-zero row); dequantize with q.float() / row_scale[:, None].
+    row_scale has one fp32 per row of the flattened input.  Forward only."""
+    _require_cuda(input)
+    k = _ops.RMSNORM if kind == "rmsnorm" else _ops.LAYERNORM
+    q, s, rs, _amax = _t.norm_fp8_scaled(k, _flat(input), None if residual is None else _flat(residual), weight, bias,
+                                         None, eps)
+    return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), rs
+
+
 class FusedRMSNorm(nn.Module):
     """torch.nn.RMSNorm-compatible module (normalized_shape, eps, elementwise_affine; parameter `weight`)."""
 

@@ -110,6 +110,31 @@ int fln_norm_forward_fp8(int kind, const void* x, const void* residual, const vo
                          float* amax, float* scale, int64_t rows, int64_t cols, int io_dtype,
                          float eps, void* stream);
 
+/* One-pass fp8-e4m3 forward with a scale the caller supplies ("delayed scaling": typically
+ * 448 / amax of the previous step).  One launch: reads x (+ residual) once, writes sum_out and
+ * q = sat_e4m3(y * *scale_in); 7 bytes per element with a residual instead of the 9 of the
+ * two-launch form above.
+ *   scale_in  one fp32 on the device, required
+ *   amax_out  one fp32 on the device or NULL: max|y| of THIS call (for the next step's scale)
+ *   mean, rstd  optional here (nothing re-reads them)
+ * Values beyond +-448 after scaling saturate.  Same shape / alignment rules as
+ * fln_norm_forward_fp8.  No counterpart in the reference. */
+int fln_norm_forward_fp8_delayed(int kind, const void* x, const void* residual, const void* gamma,
+                                 const void* beta, void* q, void* sum_out, float* mean, float* rstd,
+                                 const float* scale_in, float* amax_out, int64_t rows, int64_t cols,
+                                 int io_dtype, float eps, void* stream);
+
+/* One-pass fp8-e4m3 forward with one scale per row: row_scale[r] = 448 / max|y[r, :]| (1 for an
+ * all-zero row), q[r, :] = sat_e4m3(y[r, :] * row_scale[r]).  The row is in registers when its
+ * maximum is known, so this is also one launch and 7 bytes per element.
+ *   row_scale [rows] fp32 on the device, required (dequantize with q / row_scale[r])
+ *   amax_out  one fp32 or NULL: max|y| over the whole tensor
+ * No counterpart in the reference. */
+int fln_norm_forward_fp8_rowwise(int kind, const void* x, const void* residual, const void* gamma,
+                                 const void* beta, void* q, void* sum_out, float* mean, float* rstd,
+                                 float* row_scale, float* amax_out, int64_t rows, int64_t cols,
+                                 int io_dtype, float eps, void* stream);
+
 /* ----------------------------------------------------------------------------------
  * Backward
  * -------------------------------------------------------------------------------- */

@@ -125,6 +125,25 @@ def quant_fp8(y32):
     return q, amax, scale
 
 
+def quant_fp8_delayed(y32, scale):
+    """Quantization with a scale fixed beforehand (delayed scaling): q = saturating e4m3 of
+    y32 * scale, and amax = max |y32| of this tensor for the next step.  The torch composition
+    is (y32 * scale).clamp(-448, 448).to(float8_e4m3fn); y32.abs().max()."""
+    y32 = _c(y32).float()
+    q = e4m3_encode(y32 * torch.as_tensor(scale, dtype=torch.float32).reshape(()))
+    return q, y32.abs().max().reshape(1)
+
+
+def quant_fp8_rowwise(y32):
+    """One scale per row: scale[r] = 448 / max |y32[r]| in fp32 (1 for an all-zero row),
+    q[r] = saturating e4m3 of y32[r] * scale[r]."""
+    y32 = _c(y32).float()
+    rmax = y32.abs().amax(dim=-1)
+    scale = torch.where(rmax > 0, torch.tensor(448.0) / rmax, torch.ones_like(rmax))
+    q = e4m3_encode(y32 * scale[:, None])
+    return q, scale, rmax.max().reshape(1) if rmax.numel() else torch.zeros(1)
+
+
 def ref_g2_layernorm(x, gamma, beta, eps=1e-5, gelu=False):
     """Literal fp32 restatement of the reference's shipped kernel, summation order included."""
     x = _c(x).float()

@@ -267,6 +267,56 @@ def test_fp8_golden_fixture(golden):
     assert torch.equal(s.cpu().view(torch.int16), c["sum"].view(torch.int16))
 
 
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("rmsnorm", False), ("layernorm", True)])
+@pytest.mark.parametrize("dtype", [BF16, F16, F32])
+@pytest.mark.parametrize("shape", [(64, 8192), (257, 1024), (5, 4096)])
+def test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residual):
+    rows, cols = shape
+    x, gamma, beta, _, res = U.make_inputs(20246, rows, cols, dtype, residual=residual, outliers=True)
+    if kind == "rmsnorm":
+        beta = None
+    want = O.norm_forward(x, gamma, beta, res, kind, 1e-6)
+    y32 = want["y32"]
+
+    def check_codes(q, wq):
+        d = O.fp8_code_distance(q.check().cpu(), wq)
+        assert int(d.max()) <= 1
+        assert int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+
+    # delayed scaling: a stale scale (half of what this tensor needs, so the largest values
+    # saturate); statistics outputs are optional and left out here
+    stale = torch.tensor([2 * 448.0 / float(y32.abs().max())])
+    q = U.Guarded((rows, cols), torch.uint8)
+    s = U.Guarded((rows, cols), dtype) if residual else None
+    amax = torch.full((1,), -1.0, device="cuda")
+    capi.norm_forward_fp8_delayed(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t,
+                                  s.t if s else None, None, None, stale.cuda(), amax, 1e-6)
+    torch.cuda.synchronize()
+    wq, wamax = O.quant_fp8_delayed(y32, stale)
+    torch.testing.assert_close(amax.cpu(), wamax, rtol=1e-5, atol=0)
+    check_codes(q, wq)
+    assert int(wq.max()) >= 0x7e or int((wq & 0x7f).max()) == 0x7e  # the case does saturate
+    if residual:
+        assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
+
+    # per-row scales, with mean / rstd written as well
+    q = U.Guarded((rows, cols), torch.uint8)
+    s = U.Guarded((rows, cols), dtype) if residual else None
+    mean = torch.empty(rows, device="cuda") if kind == "layernorm" else None
+    rstd = torch.empty(rows, device="cuda")
+    rs = U.Guarded((rows,), torch.float32)
+    capi.norm_forward_fp8_rowwise(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t,
+                                  s.t if s else None, mean, rstd, rs.t, None, 1e-6)
+    torch.cuda.synchronize()
+    wq, wscale, _ = O.quant_fp8_rowwise(y32)
+    got_scale = rs.check().cpu()
+    torch.testing.assert_close(got_scale, wscale, rtol=1e-5, atol=0)
+    # codes against the quantizer run with the device's own scales (a scale that differs in
+    # the last bit moves values that sit on a rounding boundary)
+    check_codes(q, O.e4m3_encode(y32 * got_scale[:, None]))
+    torch.testing.assert_close(rstd.cpu(), want["rstd"], rtol=1e-5, atol=1e-6)
+
+
 def test_fp8_rejects_ragged_rows():
     x = torch.randn(4, 1023, device="cuda", dtype=BF16)
     q = torch.empty(4, 1023, dtype=torch.uint8, device="cuda")

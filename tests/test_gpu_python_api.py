@@ -267,6 +267,29 @@ def test_fp8_function():
     assert q2.shape == x.shape and s2.numel() == 0
 
 
+def test_fp8_one_pass_functions():
+    from fused_layernorm import fused_add_norm_fp8_delayed, fused_add_norm_fp8_rowwise
+    x = torch.randn(4, 64, 2048, device="cuda", dtype=BF16)
+    r = (0.5 * torch.randn(4, 64, 2048, device="cuda")).to(BF16)
+    w = (1 + 0.1 * torch.randn(2048, device="cuda")).to(BF16)
+    want = O.norm_forward(x.cpu().reshape(-1, 2048), w.cpu(), None, r.cpu().reshape(-1, 2048), "rmsnorm", 1e-6)
+    # step 0 measures amax with a neutral scale, step 1 quantizes with 448 / that amax
+    _, _, amax = fused_add_norm_fp8_delayed(x, torch.ones(1, device="cuda"), r, w)
+    torch.testing.assert_close(amax.cpu(), want["y32"].abs().max().reshape(1), rtol=1e-5, atol=0)
+    scale = 448.0 / amax
+    q, s, amax2 = fused_add_norm_fp8_delayed(x, scale, r, w)
+    assert q.shape == x.shape and q.dtype == torch.float8_e4m3fn and torch.equal(s, x + r) and torch.equal(amax, amax2)
+    wq, _ = O.quant_fp8_delayed(want["y32"], scale.cpu())
+    d = O.fp8_code_distance(q.view(torch.uint8).cpu().reshape(-1, 2048), wq)
+    assert int(d.max()) <= 1 and int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+    q, s, rs = fused_add_norm_fp8_rowwise(x, r, w)
+    assert rs.shape == (256,) and torch.equal(s, x + r)
+    deq = q.float().reshape(-1, 2048).cpu() / rs.cpu()[:, None]
+    assert bool(((deq - want["y32"]).abs() <= want["y32"].abs() * 0.0625 + (2.0 ** -9 / rs.cpu())[:, None]).all())
+    q3, s3, rs3 = fused_add_norm_fp8_rowwise(x, None, w, None, 1e-5, "layernorm")
+    assert s3 is None and rs3.shape == (256,)
+
+
 def test_replace_layernorm_modules_on_device():
     model = nn.Sequential(nn.Linear(256, 256), nn.LayerNorm(256), nn.GELU(), nn.LayerNorm(256)).cuda()
     x = torch.randn(16, 256, device="cuda")

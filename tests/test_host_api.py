@@ -116,7 +116,7 @@ def test_replace_layernorm_modules_shares_parameters():
 def test_operator_schemas_and_fake_tracing():
     ops = torch.ops.fused_layernorm
     for name in ["layernorm", "layernorm_gelu", "layernorm_fwd", "rmsnorm_fwd", "add_layernorm_fwd", "add_rmsnorm_fwd",
-                 "norm_fp8", "layernorm_bwd", "rmsnorm_bwd", "layernorm_bwd_f32", "cast_from_f32"]:
+                 "norm_fp8", "norm_fp8_scaled", "layernorm_bwd", "rmsnorm_bwd", "layernorm_bwd_f32", "cast_from_f32"]:
         assert hasattr(ops, name)
     assert "Tensor? gamma" in str(ops.layernorm_fwd.default._schema)
     # shape propagation through the fake implementations (what torch.compile relies on)
@@ -130,6 +130,11 @@ def test_operator_schemas_and_fake_tracing():
     assert s.shape == (6, 32) and r2.shape == (6,)
     q, s8, scale, m8, r8 = ops.norm_fp8(1, x, x, w, None, 1e-6)
     assert q.dtype == torch.float8_e4m3fn and scale.shape == (1,) and m8.numel() == 0
+    sc = torch.empty(1, device="meta")
+    q, s8, rs, amax = ops.norm_fp8_scaled(1, x, x, w, None, sc, 1e-6)  # caller's scale: no per-row scales
+    assert q.dtype == torch.float8_e4m3fn and s8.shape == (6, 32) and rs.numel() == 0 and amax.shape == (1,)
+    q, s8, rs, amax = ops.norm_fp8_scaled(1, x, None, w, None, None, 1e-6)
+    assert rs.shape == (6,) and rs.dtype == torch.float32 and s8.numel() == 0
     dxf, dgb = ops.layernorm_bwd_f32(y, x, mean, rstd, w)
     assert dgb.shape == (64,) and dgb.dtype == torch.float32
 

@@ -116,3 +116,24 @@ def test_torch_composition_matches_oracle_on_fresh_seed():
         t = O.torch_forward(x, gamma, b, res, kind, 1e-5)
         assert int(O.ulp_distance_16(a["y"], t["y"]).max()) <= 1
         assert torch.equal(a["sum"].view(torch.int16), t["sum"].view(torch.int16))
+
+
+def test_scaled_fp8_quantizers_match_torch_cast():
+    """The two one-pass quantizers (caller-supplied scale, per-row scale) against torch's own
+    e4m3 cast of the clamped product."""
+    g = torch.Generator().manual_seed(77)
+    y = torch.randn(33, 512, generator=g) * 3
+    y[3] = 0
+    y[5, 7] = 1e4  # saturates under the stale scale below
+    q, amax = O.quant_fp8_delayed(y, 20.0)
+    want = (y * 20.0).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(q, want)
+    assert float(amax) == float(y.abs().max())
+    q, scale, amax = O.quant_fp8_rowwise(y)
+    rmax = y.abs().amax(-1)
+    # IEEE fp32 division (via float64, which rounds to the same fp32); `448.0 / tensor` in
+    # torch is a reciprocal and a multiply, i.e. two roundings
+    assert torch.equal(scale, torch.where(rmax > 0, (448.0 / rmax.double()).float(), torch.ones_like(rmax)))
+    want = (y * scale[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(q, want)
+    assert float(scale[3]) == 1.0 and int(q[3].max()) == 0
