@@ -440,7 +440,7 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
   // large aligned problems: persistent bulk-async pipeline for stage 1
   const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
   const int64_t pipeP =
-      (aligned && p.dres_in == nullptr) ? bwd_pipeline_partial_rows(KIND, dt, p.rows, p.cols) : 0;
+      aligned ? bwd_pipeline_partial_rows(KIND, dt, p.rows, p.cols, p.dres_in != nullptr) : 0;
   if (pipeP > 0) {
     if (want_params) {
       const size_t need = (size_t)pipeP * NR * p.cols * sizeof(float);
@@ -521,8 +521,10 @@ static size_t ws_bytes_typed(int64_t rows, int cols) {
   if (R.P > P) P = R.P;
   if (R1.P > P) P = R1.P;
   const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
-  const int64_t pipeP = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols);
+  const int64_t pipeP = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols, false);
   if (pipeP > P) P = pipeP;
+  const int64_t pipeP3 = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols, true);
+  if (pipeP3 > P) P = pipeP3;
   // + one 16-byte slot for the grid barrier of the fused column reduce
   return (((size_t)P * 2 * cols * sizeof(float) + 15) & ~(size_t)15) + 16;
 }

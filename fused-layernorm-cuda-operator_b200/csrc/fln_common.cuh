@@ -497,7 +497,7 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
 // column reduce); otherwise the caller reduces p.partials.
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);
 // partial rows the pipelined backward writes for this shape (0 = not applicable)
-int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols);
+int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, bool with_dres);
 
 // ------------------------------------------------------------------------------------
 // host side: launch plan

@@ -489,7 +489,10 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb) 
 // Per element: two widening shifts, (x - mean) * rstd, g = dy * gamma, two running sums,
 // then dx = rstd * ((g - c2) - xhat * c1) and the two column accumulators.
 // ----------------------------------------------------------------------------------------
-template <typename T, int K, int KIND, bool FULL, bool FUSE>
+// DRES: an incoming gradient of the residual stream (same shape as dx) is staged as a third
+// tensor and added into dx; each thread parks its (still packed) part in registers before the
+// barrier that releases the stage.
+template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES>
 __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, const PipeGeom g) {
   constexpr int VEC = 16 / sizeof(T);
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
@@ -519,9 +522,11 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     const int64_t left = p.rows - row0;
     const uint32_t bytes = (uint32_t)(left < g.R ? left : g.R) * g.row_bytes;
     unsigned char* dst = stages + (size_t)s * g.stage_stride;
-    mbar_expect_tx(&full[s], 2 * bytes);
+    mbar_expect_tx(&full[s], (DRES ? 3 : 2) * bytes);
     bulk_g2s(dst, reinterpret_cast<const T*>(p.dy) + row0 * p.cols, bytes, &full[s]);
     bulk_g2s(dst + g.second_off, reinterpret_cast<const T*>(p.x) + row0 * p.cols, bytes, &full[s]);
+    if (DRES)
+      bulk_g2s(dst + 2 * g.second_off, reinterpret_cast<const T*>(p.dres_in) + row0 * p.cols, bytes, &full[s]);
   };
   if (tid == 0) {
     const int pre = my_tiles < S ? my_tiles : S;
@@ -577,12 +582,14 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     const float nmr = -mean * rstd;
 
     float xh[K][VEC], dyf[K][VEC];
+    Pack<T, VEC> dres[DRES ? K : 1];
     float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
         unpack<T, VEC>(stage_vec<T>(st + k * k_off), dyf[k]);
         unpack<T, VEC>(stage_vec<T>(st + g.second_off + k * k_off), xh[k]);
+        if (DRES) dres[k] = ld_smem16<T>(st + 2 * g.second_off + k * k_off);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
           xh[k][e] = sizeof(T) == 2 ? fmaf(xh[k][e], rstd, nmr) : (xh[k][e] - mean) * rstd;
@@ -632,6 +639,12 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
             // (dy * gamma) - c2 bit for bit there and saves the multiply
             const float gc = sizeof(T) == 2 ? fmaf(dyf[k][e], gam[k][e], -c2) : dyf[k][e] * gam[k][e] - c2;
             o[e] = rstd * fmaf(xh[k][e], nc1, gc);
+          }
+          if (DRES) {
+            float dr[VEC];
+            unpack<T, VEC>(dres[k], dr);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[e] += dr[e];
           }
           Pack<T, VEC> out;
           pack<T, VEC>(o, out);
@@ -1034,11 +1047,11 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
 template <typename T, int KIND>
 static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
-#define FLN_LAUNCH(KK, FF)                                                                   \
+#define FLN_LAUNCH(KK, FF, DR)                                                               \
   {                                                                                          \
     if (p.sync != nullptr) {                                                                 \
       /* the grid barrier needs every CTA resident: cooperative launch */                   \
-      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, true>;        \
+      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, true, DR>;    \
       if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                           \
       cudaLaunchConfig_t cfg;                                                                \
       memset(&cfg, 0, sizeof(cfg));                                                          \
@@ -1056,7 +1069,7 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
         return FLN_ERR_LAUNCH;                                                               \
       }                                                                                      \
     } else {                                                                                 \
-      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, false>;       \
+      auto kern = norm_bwd_pipe_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND, FF, false, DR>;   \
       if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                           \
       kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                       \
     }                                                                                        \
@@ -1071,8 +1084,11 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   case KK:                                                 \
     if (VEC * KK > 16) return FLN_PIPE_NOT_APPLICABLE;     \
     if (P.full && P.rpt == 2) FLN_LAUNCH2(KK)              \
-    else if (P.full) FLN_LAUNCH(KK, true)                  \
-    else FLN_LAUNCH(KK, false)                             \
+    else if (p.dres_in != nullptr) {                       \
+      if (P.full) FLN_LAUNCH(KK, true, true)               \
+      else FLN_LAUNCH(KK, false, true)                     \
+    } else if (P.full) FLN_LAUNCH(KK, true, false)         \
+    else FLN_LAUNCH(KK, false, false)                      \
     break;
   switch (P.K) {
     FLN_CASE(1) FLN_CASE(2) FLN_CASE(4)
@@ -1089,7 +1105,8 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
 // Backward plan.  The two-rows-per-barrier kernel measured slower on B200 (257 vs 179 us at
 // 16384 x 8192 bf16: it spills at 128 registers and leaves room for only 3 stages), so it is
 // selected only by path override 4, for A/B timing.
-static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es) {
+static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
+  if (with_dres) return plan_pipeline(true, rows, cols, es, 3, 1);
   if (g_path_override.load(std::memory_order_relaxed) == 4) {
     PipePlan P2 = plan_pipeline(true, rows, cols, es, 2, 2);
     if (P2.ok && P2.full) return P2;
@@ -1097,10 +1114,10 @@ static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es) {
   return plan_pipeline(true, rows, cols, es, 2, 1);
 }
 
-int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols) {
+int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, bool with_dres) {
   (void)kind;
   const int es = dtype == FLN_F32 ? 4 : 2;
-  PipePlan P = plan_bwd_pipeline(rows, cols, es);
+  PipePlan P = plan_bwd_pipeline(rows, cols, es, with_dres);
   if (!pipeline_wanted(P, rows)) return 0;
   return (int64_t)P.grid * (P.g.R / P.rpt);
 }
@@ -1132,8 +1149,8 @@ static unsigned long long next_launch_token() {
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t st, bool* reduced) {
   const int es = dtype == FLN_F32 ? 4 : 2;
   *reduced = false;
-  PipePlan P = plan_bwd_pipeline(p0.rows, p0.cols, es);
-  if (!pipeline_wanted(P, p0.rows) || p0.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
+  PipePlan P = plan_bwd_pipeline(p0.rows, p0.cols, es, p0.dres_in != nullptr);
+  if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   BwdParams p = p0;
   p.nv = p.cols / (16 / es);
   // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the

@@ -500,6 +500,34 @@ def test_kernel_families_agree_with_oracle(path_override, shape, dtype, kind, mo
     U.assert_param_grads_close(gb["dgb_f32"][:cols], wb["dgamma64"], wb["abs64"][0], rows)
     if kind == "layernorm":
         U.assert_param_grads_close(gb["dgb_f32"][cols:], wb["dbeta64"], wb["abs64"][1], rows)
+    # with an incoming gradient of the residual stream added into dx (same parameter sums)
+    gr = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=res)
+    wr = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, res, kind)
+    if dtype == F32:
+        torch.testing.assert_close(gr["dx"], wr["dx32"], rtol=1e-5, atol=1e-5)
+    else:
+        U.assert_out_close(gr["dx"], wr["dx"], dtype)
+    assert torch.equal(gr["dgb_f32"], gb["dgb_f32"])
+    assert capi.lib().fln_device_status() == 0
+
+
+def test_pipelined_backward_adds_residual_gradient_in_place():
+    """dx may be the buffer that holds the incoming residual-stream gradient."""
+    rows, cols = 8192, 4096
+    x, gamma, beta, dy, res = U.make_inputs(77, rows, cols, BF16, residual=True)
+    f = O.norm_forward(x, gamma, beta)
+    xd, dyd, gd = x.cuda(), dy.cuda(), gamma.cuda()
+    md, rd = f["mean"].cuda(), f["rstd"].cuda()
+    ws = torch.empty(capi.backward_workspace_bytes(rows, cols, BF16) // 4, device="cuda")
+    sep = torch.empty(rows, cols, dtype=BF16, device="cuda")
+    capi.norm_backward(capi.LAYERNORM, dyd, xd, md, rd, gd, res.cuda(), sep, None, None, None, ws)
+    inplace = res.cuda().clone()
+    capi.norm_backward(capi.LAYERNORM, dyd, xd, md, rd, gd, inplace, inplace, None, None, None, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(sep, inplace)
+    idx = torch.tensor([0, 17, 4095, 8191])
+    want = O.norm_backward(dy[idx], x[idx], f["mean"][idx], f["rstd"][idx], gamma, res[idx])
+    U.assert_out_close(sep[idx.cuda()].cpu(), want["dx"], BF16)
     assert capi.lib().fln_device_status() == 0
 
 
