@@ -220,6 +220,144 @@ __global__ void __launch_bounds__(256) norm_bwd_cols_generic_kernel(const BwdPar
 }
 
 // ----------------------------------------------------------------------------------------
+// Rows too long for the register-resident and pipelined kernels (more than 16 columns per
+// thread of a 512-thread CTA), but aligned and a whole number of 16-byte vectors: the same
+// two kernels with 128-bit accesses.
+//   dx:   one CTA per row; pass 1 streams the row for the two row sums, pass 2 re-reads it
+//         (L1 / L2 hits: a row is at most a few hundred KB) and writes dx.
+//   cols: thread = one vector of columns, CTA row blockIdx.y walks rows y, y + P, ... with
+//         four rows in flight and writes one partial row.
+// dy and x are read from HBM twice (10 instead of 6 bytes per element).  Running the pair
+// over L2-sized chunks of rows so that the second read hits the 126 MB L2 was measured
+// slower (744 vs 480 us at 21824 x 12288 bf16): every chunk has to add into the partial rows,
+// and that traffic outweighs the saved reads.
+// ----------------------------------------------------------------------------------------
+template <typename T, int KIND>
+__global__ void __launch_bounds__(512) norm_bwd_dx_wide_kernel(const BwdParams p) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
+  __shared__ float s_red[NR * 32];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * (int64_t)p.cols;
+  const T* __restrict__ dyr = reinterpret_cast<const T*>(p.dy) + base;
+  const T* __restrict__ xr = reinterpret_cast<const T*>(p.x) + base;
+  const T* __restrict__ gp = reinterpret_cast<const T*>(p.gamma);
+  const float mean = KIND == FLN_LAYERNORM ? __ldg(p.mean + row) : 0.f;
+  const float rstd = __ldg(p.rstd + row);
+  const int nv = p.cols / VEC;
+  float r0[2] = {0.f, 0.f}, r1[2] = {0.f, 0.f};
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float dy[VEC], xx[VEC], gg[VEC];
+    unpack<T, VEC>(ld_plain<T, VEC>(dyr + (int64_t)v * VEC), dy);
+    unpack<T, VEC>(ld_plain<T, VEC>(xr + (int64_t)v * VEC), xx);
+    if (gp != nullptr) {
+      unpack<T, VEC>(ld_param<T, VEC>(gp + (int64_t)v * VEC), gg);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) gg[e] = 1.f;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float g = dy[e] * gg[e];
+      r0[e & 1] = fmaf(g, (xx[e] - mean) * rstd, r0[e & 1]);
+      if (KIND == FLN_LAYERNORM) r1[e & 1] += g;
+    }
+  }
+  float red[NR];
+  red[0] = r0[0] + r0[1];
+  if (KIND == FLN_LAYERNORM) red[NR - 1] = r1[0] + r1[1];
+  group_reduce_sum<NR>(red, blockDim.x, s_red);
+  const float inv_n = 1.0f / (float)p.cols;
+  const float nc1 = -(red[0] * inv_n);
+  const float c2 = KIND == FLN_LAYERNORM ? red[NR - 1] * inv_n : 0.f;
+  T* __restrict__ dxr = reinterpret_cast<T*>(p.dx) + base;
+  const T* __restrict__ drr = p.dres_in ? reinterpret_cast<const T*>(p.dres_in) + base : nullptr;
+  for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+    float dy[VEC], xx[VEC], gg[VEC], o[VEC];
+    unpack<T, VEC>(ld_plain<T, VEC>(dyr + (int64_t)v * VEC), dy);
+    unpack<T, VEC>(ld_plain<T, VEC>(xr + (int64_t)v * VEC), xx);
+    if (gp != nullptr) {
+      unpack<T, VEC>(ld_param<T, VEC>(gp + (int64_t)v * VEC), gg);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) gg[e] = 1.f;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o[e] = rstd * fmaf((xx[e] - mean) * rstd, nc1, dy[e] * gg[e] - c2);
+    if (drr != nullptr) {
+      float dr[VEC];
+      unpack<T, VEC>(ld_stream<T, VEC>(drr + (int64_t)v * VEC), dr);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o[e] += dr[e];
+    }
+    Pack<T, VEC> out;
+    pack<T, VEC>(o, out);
+    st_stream<T, VEC>(dxr + (int64_t)v * VEC, out);
+  }
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(128) norm_bwd_cols_wide_kernel(const BwdParams p) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= p.cols / VEC) return;
+  const T* __restrict__ dyp = reinterpret_cast<const T*>(p.dy) + (int64_t)v * VEC;
+  const T* __restrict__ xp = reinterpret_cast<const T*>(p.x) + (int64_t)v * VEC;
+  float ag[VEC], ab[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    ag[e] = 0.f;
+    ab[e] = 0.f;
+  }
+  const int64_t end = p.rows;
+  const int64_t step = gridDim.y;
+  int64_t r = blockIdx.y;
+  for (; r + 3 * step < end; r += 4 * step) {
+    Pack<T, VEC> qd[4], qx[4];
+    float mu[4], rs[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t rr = r + j * step;
+      qd[j] = ld_stream<T, VEC>(dyp + rr * (int64_t)p.cols);
+      qx[j] = ld_stream<T, VEC>(xp + rr * (int64_t)p.cols);
+      mu[j] = KIND == FLN_LAYERNORM ? __ldg(p.mean + rr) : 0.f;
+      rs[j] = __ldg(p.rstd + rr);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float dy[VEC], xx[VEC];
+      unpack<T, VEC>(qd[j], dy);
+      unpack<T, VEC>(qx[j], xx);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        ag[e] = fmaf(dy[e], (xx[e] - mu[j]) * rs[j], ag[e]);
+        if (KIND == FLN_LAYERNORM) ab[e] += dy[e];
+      }
+    }
+  }
+  for (; r < end; r += step) {
+    float dy[VEC], xx[VEC];
+    unpack<T, VEC>(ld_stream<T, VEC>(dyp + r * (int64_t)p.cols), dy);
+    unpack<T, VEC>(ld_stream<T, VEC>(xp + r * (int64_t)p.cols), xx);
+    const float mu = KIND == FLN_LAYERNORM ? __ldg(p.mean + r) : 0.f;
+    const float rs = __ldg(p.rstd + r);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      ag[e] = fmaf(dy[e], (xx[e] - mu) * rs, ag[e]);
+      if (KIND == FLN_LAYERNORM) ab[e] += dy[e];
+    }
+  }
+  float* __restrict__ pg = p.partials + (int64_t)blockIdx.y * (NR * p.cols) + (int64_t)v * VEC;
+#pragma unroll
+  for (int e = 0; e < VEC; e += 4) {
+    *reinterpret_cast<float4*>(pg + e) = make_float4(ag[e], ag[e + 1], ag[e + 2], ag[e + 3]);
+    if (KIND == FLN_LAYERNORM)
+      *reinterpret_cast<float4*>(pg + p.cols + e) = make_float4(ab[e], ab[e + 1], ab[e + 2], ab[e + 3]);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Stage 2: out[c] = sum_p partials[p][c], c in [0, ncols).  A warp reads 32 consecutive
 // columns of one partial row; the 8 warps of a CTA take rows p = w, w+8, ... and their
 // sums are combined in warp order.
@@ -347,6 +485,7 @@ struct BwdLaunch {
   int64_t row_groups;
   int64_t grid;  // stage-1 CTAs (register path) or partial rows (generic path)
   int64_t P;     // partial rows in the workspace
+  bool wide;     // long aligned rows: the vectorised, L2-chunked pair of kernels
 };
 
 template <typename T, int VEC, int K, int KIND>
@@ -388,6 +527,19 @@ template <typename T, int KIND>
 static BwdLaunch plan_bwd(int64_t rows, int cols, bool aligned) {
   BwdLaunch L;
   L.pl = make_plan(true, rows, cols, (int)sizeof(T), aligned);
+  L.wide = false;
+  if (L.pl.generic && aligned && cols % (16 / (int)sizeof(T)) == 0 && (cols * (int64_t)sizeof(T)) % 16 == 0) {
+    // vectorised long-row kernels: enough partial rows for about 8 CTAs of 128 threads per SM
+    L.wide = true;
+    L.row_groups = rows;
+    const int nv = cols / (16 / (int)sizeof(T));
+    int64_t Pw = 8LL * sm_count() / ((nv + 127) / 128);
+    if (Pw < 1) Pw = 1;
+    if (Pw > 256) Pw = 256;
+    L.P = rows < Pw ? rows : Pw;
+    L.grid = rows;
+    return L;
+  }
   if (L.pl.generic) {
     L.row_groups = rows;
     int64_t Pmax = 4LL * sm_count() / ((cols + 255) / 256);
@@ -484,7 +636,18 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
   p.tpr = L.pl.tpr;
   p.log2_tpr = L.pl.log2_tpr;
   p.row_groups = L.row_groups;
-  if (L.pl.generic) {
+  if (L.wide) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const unsigned gx = (unsigned)((p.cols / VEC + 127) / 128);
+    if (p.dx != nullptr) {
+      norm_bwd_dx_wide_kernel<T, KIND><<<(unsigned)p.rows, 512, 0, st>>>(p);
+      FLN_CHECK_LAUNCH();
+    }
+    if (want_params) {
+      norm_bwd_cols_wide_kernel<T, KIND><<<dim3(gx, (unsigned)L.P), 128, 0, st>>>(p);
+      FLN_CHECK_LAUNCH();
+    }
+  } else if (L.pl.generic) {
     if (p.dx != nullptr) {
       norm_bwd_dx_generic_kernel<T, KIND><<<(unsigned)p.rows, 512, 0, st>>>(p);
       FLN_CHECK_LAUNCH();

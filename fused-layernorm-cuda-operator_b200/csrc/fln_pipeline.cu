@@ -112,12 +112,20 @@ __device__ __forceinline__ Pack<T, 16 / sizeof(T)> ld_smem16(const unsigned char
 // load above (measured 246.8 vs 285.7 us for the bf16 forward + backward).  fp32: by reference,
 // which lets the compiler schedule four 32-bit loads; that form measured faster for fp32
 // (backward 245 vs 277 us at 16384 x 8192), where the kernel is HBM-bound anyway.
-template <typename T>
+// Vectors shorter than 16 bytes (row lengths 3, 5 or 7 times a power of two are split into 8- or
+// 4-byte vectors so that they divide evenly over the threads) are read with one load of that
+// width.
+template <typename T, int VEC = 16 / sizeof(T)>
 __device__ __forceinline__ decltype(auto) stage_vec(const unsigned char* p) {
-  if constexpr (sizeof(T) == 4) {
+  if constexpr (VEC * sizeof(T) == 16 && sizeof(T) == 4) {
     return (*reinterpret_cast<const Pack<T, 4>*>(p));
-  } else {
+  } else if constexpr (VEC * sizeof(T) == 16) {
     return ld_smem16<T>(p);
+  } else {
+    using R = typename Raw<sizeof(T) * VEC>::type;
+    Pack<T, VEC> out;
+    *reinterpret_cast<R*>(&out) = *reinterpret_cast<const R*>(p);
+    return out;
   }
 }
 
@@ -187,9 +195,9 @@ __device__ __forceinline__ void grid_depart(unsigned long long* w, unsigned int 
 // MODE 0: general (bounds-checked); 1: FULL (no predication in the loop); 2: FULL and the
 // CTA owns exactly one row, which allows the one-barrier LayerNorm statistics below (measured
 // no faster on B200, so the launcher does not select it).
-template <typename TI, typename TO, int K, int KIND, int ACT, int MODE>
+template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16>
 __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
-  constexpr int VEC = 16 / sizeof(TI);
+  constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr bool FULL = MODE >= 1;
   constexpr bool ONE = MODE == 2 && KIND == FLN_LAYERNORM;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -252,8 +260,8 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   uint32_t phase = 0;
   int64_t row = (int64_t)blockIdx.x * g.R + r_in;
   const int64_t row_step = (int64_t)gridDim.x * g.R;
-  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * 16u;
-  const uint32_t k_off = (uint32_t)tpr * 16u;
+  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * (uint32_t)VB;
+  const uint32_t k_off = (uint32_t)tpr * (uint32_t)VB;
   for (int i = 0; i < my_tiles; ++i, row += row_step) {
     const bool landed = mbar_wait_bounded(&full[s], phase);
     const bool row_ok = FULL ? true : row < p.rows;
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<TI, VEC>(stage_vec<TI>(st + k * k_off), f[k]);
+        unpack<TI, VEC>(stage_vec<TI, VEC>(st + k * k_off), f[k]);
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) f[k][e] = 0.f;
@@ -277,7 +285,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       for (int k = 0; k < K; ++k) {
         if (FULL || (row_ok && vok[k])) {
           float r[VEC];
-          unpack<TI, VEC>(stage_vec<TI>(st + g.second_off + k * k_off), r);
+          unpack<TI, VEC>(stage_vec<TI, VEC>(st + g.second_off + k * k_off), r);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) f[k][e] += r[e];
           // the sum is rounded to the I/O type first: that value is normalized and stored
@@ -294,7 +302,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     if (KIND == FLN_LAYERNORM) {
       // shift by element 0 of the row (a broadcast read of the stage): a constant row then
       // sums to exactly zero whatever its magnitude, and |mean| >> std costs no accuracy
-      const unsigned char* st0 = st - (size_t)lane_r * 16;
+      const unsigned char* st0 = st - (size_t)lane_r * VB;
       float c = Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0));
       if (has_res)
         c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0 + g.second_off))));
@@ -492,9 +500,9 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb) 
 // DRES: an incoming gradient of the residual stream (same shape as dx) is staged as a third
 // tensor and added into dx; each thread parks its (still packed) part in registers before the
 // barrier that releases the stage.
-template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES>
+template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES, int VB = 16>
 __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, const PipeGeom g) {
-  constexpr int VEC = 16 / sizeof(T);
+  constexpr int VEC = VB / sizeof(T);  // even
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -560,8 +568,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 
   int s = 0;
   uint32_t phase = 0;
-  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * 16u;
-  const uint32_t k_off = (uint32_t)tpr * 16u;
+  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * (uint32_t)VB;
+  const uint32_t k_off = (uint32_t)tpr * (uint32_t)VB;
   for (int i = 0; i < my_tiles; ++i, row += row_step) {
     const bool row_ok = FULL ? true : row < p.rows;
     const float mean = mean_n, rstd = rstd_n;
@@ -587,9 +595,9 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
-        unpack<T, VEC>(stage_vec<T>(st + k * k_off), dyf[k]);
-        unpack<T, VEC>(stage_vec<T>(st + g.second_off + k * k_off), xh[k]);
-        if (DRES) dres[k] = ld_smem16<T>(st + 2 * g.second_off + k * k_off);
+        unpack<T, VEC>(stage_vec<T, VEC>(st + k * k_off), dyf[k]);
+        unpack<T, VEC>(stage_vec<T, VEC>(st + g.second_off + k * k_off), xh[k]);
+        if (DRES) dres[k] = stage_vec<T, VEC>(st + 2 * g.second_off + k * k_off);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
           xh[k][e] = sizeof(T) == 2 ? fmaf(xh[k][e], rstd, nmr) : (xh[k][e] - mean) * rstd;
@@ -673,13 +681,22 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     for (int k = 0; k < K; ++k) {
       const int iv = lane_r + k * tpr;
       if (vok[k]) {
+        if constexpr (VEC % 4 == 0) {
 #pragma unroll
-        for (int e = 0; e < VEC; e += 4) {
-          *reinterpret_cast<float4*>(pg + (int64_t)iv * VEC + e) =
-              make_float4(acc_g[k][e], acc_g[k][e + 1], acc_g[k][e + 2], acc_g[k][e + 3]);
-          if (KIND == FLN_LAYERNORM)
-            *reinterpret_cast<float4*>(pg + p.cols + (int64_t)iv * VEC + e) =
-                make_float4(acc_b[k][e], acc_b[k][e + 1], acc_b[k][e + 2], acc_b[k][e + 3]);
+          for (int e = 0; e < VEC; e += 4) {
+            *reinterpret_cast<float4*>(pg + (int64_t)iv * VEC + e) =
+                make_float4(acc_g[k][e], acc_g[k][e + 1], acc_g[k][e + 2], acc_g[k][e + 3]);
+            if (KIND == FLN_LAYERNORM)
+              *reinterpret_cast<float4*>(pg + p.cols + (int64_t)iv * VEC + e) =
+                  make_float4(acc_b[k][e], acc_b[k][e + 1], acc_b[k][e + 2], acc_b[k][e + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; e += 2) {
+            *reinterpret_cast<float2*>(pg + (int64_t)iv * VEC + e) = make_float2(acc_g[k][e], acc_g[k][e + 1]);
+            if (KIND == FLN_LAYERNORM)
+              *reinterpret_cast<float2*>(pg + p.cols + (int64_t)iv * VEC + e) = make_float2(acc_b[k][e], acc_b[k][e + 1]);
+          }
         }
       }
     }
@@ -889,6 +906,7 @@ struct PipePlan {
   bool ok;
   bool full;  // branch-free instantiation applies
   int rpt;    // rows per thread per barrier (backward: 1 or 2)
+  int vb;     // bytes per vector: 16, or 8 / 4 where that makes the row divide evenly
   int K;
   int threads;
   int grid;
@@ -937,6 +955,35 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
     tpr = t;
   }
   if (K == 0) return P;
+  // Row lengths 3, 5 or 7 times a power of two (768, 1280, 2560, 5120, 6144, 12288 ...) do not
+  // divide over a power-of-two number of threads with a power-of-two number of 16-byte vectors
+  // each; the padded plan above would run them through the bounds-checked kernel with a
+  // quarter or more of the lanes idle.  Look for an exact fit with K in {3, 5, 7} and, if
+  // need be, 8- or 4-byte vectors; the branch-free instantiation then applies.
+  int vb = 16;
+  if (fK == 0 && rpt == 1 && (int64_t)K * tpr != nv) {
+    const int cap_elems = backward ? 16 : 32;
+    const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
+    int best_elems = 0;
+    for (int cvb = 16; cvb >= min_vb; cvb >>= 1) {
+      const int cvec = cvb / elem_bytes;
+      if (cols % cvec != 0) continue;
+      const int cnv = cols / cvec;
+      for (int ck = 3; ck <= 7; ck += 2) {
+        if (ck * cvec > cap_elems || cnv % ck != 0) continue;
+        const int t = cnv / ck;
+        if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
+        const int thr = t > cta_threads ? t : cta_threads;
+        if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these
+        if (ck * cvec > best_elems) {
+          best_elems = ck * cvec;
+          K = ck;
+          tpr = t;
+          vb = cvb;
+        }
+      }
+    }
+  }
   const int threads = tpr > cta_threads ? tpr : cta_threads;
   const int R = (threads / tpr) * rpt;
   const uint32_t row_bytes = (uint32_t)cols * elem_bytes;
@@ -954,7 +1001,8 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
   }
   P.ok = true;
   P.rpt = rpt;
-  P.full = tpr >= 32 && (int64_t)K * tpr == nv && rows % R == 0;
+  P.full = tpr >= 32 && (int64_t)K * tpr == cols / (vb / elem_bytes) && rows % R == 0;
+  P.vb = vb;
   P.K = K;
   P.threads = threads;
   P.smem = kSmemHeader + (size_t)S * stage;
@@ -993,8 +1041,33 @@ static int set_smem(F kernel, size_t smem) {
   return FLN_OK;
 }
 
+// one branch-free instantiation with an odd K and / or short vectors; combinations that make no
+// sense for the type (too many elements per thread, vectors shorter than four elements) are
+// not instantiated
+template <typename TI, typename TO, int KIND, int ACT, int KK, int VB>
+static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  constexpr int VEC = VB / (int)sizeof(TI);
+  if constexpr (VEC >= 4 && KK * VEC <= 32) {
+    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 1, VB>;
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
+    FLN_CHECK_LAUNCH();
+    return FLN_OK;
+  } else {
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
+}
+
 template <typename TI, typename TO, int KIND, int ACT>
 static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) {
+    if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
+#define FLN_ODD(KK, VBB) \
+  if (P.K == KK && P.vb == VBB) return fwd_pipe_odd<TI, TO, KIND, ACT, KK, VBB>(p, P, st);
+    FLN_ODD(3, 16) FLN_ODD(5, 16) FLN_ODD(7, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8)
+#undef FLN_ODD
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
 #define FLN_LAUNCH(KK, FF)                                                                   \
   {                                                                                          \
     auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, FF>;                             \
@@ -1037,16 +1110,66 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
   PipePlan P = plan_pipeline(false, p0.rows, p0.cols, es, p0.res != nullptr ? 2 : 1);
   if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   FwdParams p = p0;
-  p.nv = p.cols / (16 / es);
+  p.nv = p.cols / (P.vb / es);
   if (io_dtype == FLN_F32 && out_dtype == FLN_F32) return fwd_pipe_typed<float, float>(kind, act, p, P, st);
   if (io_dtype == FLN_F32 && out_dtype == FLN_BF16) return fwd_pipe_typed<float, __nv_bfloat16>(kind, act, p, P, st);
   if (io_dtype == FLN_BF16) return fwd_pipe_typed<__nv_bfloat16, __nv_bfloat16>(kind, act, p, P, st);
   return fwd_pipe_typed<__half, __half>(kind, act, p, P, st);
 }
 
+template <typename KernelT>
+static int launch_bwd_kernel(KernelT kern, const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
+  if (p.sync != nullptr) {
+    // the grid barrier needs every CTA resident: cooperative launch
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)P.grid);
+    cfg.blockDim = dim3((unsigned)P.threads);
+    cfg.dynamicSmemBytes = P.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, p, P.g) != cudaSuccess) {
+      cudaGetLastError();
+      return FLN_ERR_LAUNCH;
+    }
+  } else {
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
+  }
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
+}
+
+// branch-free instantiations with an odd K and short vectors (see plan_pipeline)
+template <typename T, int KIND, int KK, int VB>
+static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  constexpr int VEC = VB / (int)sizeof(T);
+  if constexpr (VEC >= 2 && KK * VEC <= 16) {
+    const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
+    if (fuse && dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB>, p, P, st);
+    if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB>, p, P, st);
+    if (dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, true, VB>, p, P, st);
+    return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB>, p, P, st);
+  } else {
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
+}
+
 template <typename T, int KIND>
 static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
+  if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) {
+    if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
+#define FLN_ODD(KK, VBB) \
+  if (P.K == KK && P.vb == VBB) return bwd_pipe_odd<T, KIND, KK, VBB>(p, P, st);
+    FLN_ODD(3, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8) FLN_ODD(3, 4) FLN_ODD(5, 4) FLN_ODD(7, 4)
+#undef FLN_ODD
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
 #define FLN_LAUNCH(KK, FF, DR)                                                               \
   {                                                                                          \
     if (p.sync != nullptr) {                                                                 \
@@ -1152,7 +1275,7 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
   PipePlan P = plan_bwd_pipeline(p0.rows, p0.cols, es, p0.dres_in != nullptr);
   if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   BwdParams p = p0;
-  p.nv = p.cols / (16 / es);
+  p.nv = p.cols / (P.vb / es);
   // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the
   // one-row kernel, stage memory large enough for the 16 x 128 floats of the combine step.
   const bool fuse = p.sync != nullptr && p.partials != nullptr && P.rpt == 1 && P.grid <= usable_sms() &&

@@ -56,7 +56,8 @@ class GraphedLayerNorm:
 
 
 class GraphedLayerNormStep:
-    """forward + backward (dx, dgamma, dbeta) on fixed buffers as one graph of three kernels."""
+    """forward + backward (dx, dgamma, dbeta) on fixed buffers as one graph (two kernels where the
+    backward reduces dgamma / dbeta in its own tail, three otherwise)."""
 
     def __init__(self, x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5):
         rows, cols = x.shape

@@ -3,8 +3,11 @@
 Same classes, functions, argument names and error behaviour as the reference's
 fused_layernorm/layernorm.py (FusedLayerNormFunction :31-109, FusedLayerNorm :112-231,
 fused_layer_norm :234-266, replace_/restore_torch_layernorm :270-280), with these differences:
-  * the autograd Function runs on the registered operators fused_layernorm::layernorm_fwd /
-    layernorm_bwd, so it traces under torch.compile, and it really has a backward kernel;
+  * the autograd Function really has a backward kernel.  Under torch.compile it runs on the
+    registered operators fused_layernorm::layernorm_fwd / layernorm_bwd (so it traces without
+    graph breaks); in eager mode it calls the extension's forward / backward directly, as the
+    reference does, because a registered operator with a Python autograd formula costs
+    15 - 20 us of dispatch per call, more than the kernel at the latency-bound shapes;
   * inputs of any rank are handled by flattening (the reference hands rank >= 4 and
     multi-dimensional normalized_shape to F.layer_norm, :189-193, :265-266);
   * there is no CPU or pure-PyTorch fallback: CPU tensors raise, and importing this module
@@ -57,7 +60,10 @@ class FusedLayerNormFunction(Function):
             raise ValueError(f"normalized_shape {normalized_shape} doesn't match input shape {input.shape}")
         _require_cuda(input)
         input = input.contiguous()
-        output, mean, rstd = _torch_ops.layernorm_fwd(input, weight, bias, eps)
+        if torch.compiler.is_compiling():
+            output, mean, rstd = _torch_ops.layernorm_fwd(input, weight, bias, eps)
+        else:
+            output, mean, rstd = fused_layernorm_cuda.forward(input, weight, bias, eps)
         ctx.save_for_backward(input, weight, bias, mean, rstd)
         ctx.normalized_shape = normalized_shape
         ctx.eps = eps
@@ -70,10 +76,14 @@ class FusedLayerNormFunction(Function):
         needs_input_grad = ctx.needs_input_grad[0]
         needs_weight_grad = ctx.needs_input_grad[2] if weight is not None else False
         needs_bias_grad = ctx.needs_input_grad[3] if bias is not None else False
-        dx, dw, db = _torch_ops.layernorm_bwd(grad_output, input, mean, rstd, weight, None, needs_input_grad,
-                                              needs_weight_grad, needs_bias_grad)
-        none_if_empty = _ops._none_if_empty
-        return none_if_empty(dx), None, none_if_empty(dw), none_if_empty(db), None
+        if torch.compiler.is_compiling():
+            dx, dw, db = _torch_ops.layernorm_bwd(grad_output, input, mean, rstd, weight, None, needs_input_grad,
+                                                  needs_weight_grad, needs_bias_grad)
+            none_if_empty = _ops._none_if_empty
+            return none_if_empty(dx), None, none_if_empty(dw), none_if_empty(db), None
+        dx, dw, db = fused_layernorm_cuda.backward(grad_output, input, mean, rstd, weight, bias,
+                                                   [needs_input_grad, needs_weight_grad, needs_bias_grad])
+        return dx, None, dw, db, None
 
 
 def _apply_flat(input, normalized_shape, weight, bias, eps):
@@ -119,6 +129,16 @@ class FusedLayerNorm(nn.Module):
             nn.init.zeros_(self.bias)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
+        if (input.dim() == 2 and len(self.normalized_shape) == 1 and input.is_cuda and not torch.compiler.is_compiling()
+                and input.size(1) == self.normalized_shape[0] and input.is_contiguous()
+                and not (torch.is_grad_enabled() and (input.requires_grad or (self.weight is not None and (
+                    self.weight.requires_grad or self.bias.requires_grad))))):
+            # inference: nothing to record, one call into the extension
+            return fused_layernorm_cuda.layernorm(input, self.weight, self.bias, self.eps)
+        if (input.dim() == 2 and len(self.normalized_shape) == 1 and input.is_cuda and not torch.compiler.is_compiling()
+                and input.size(1) == self.normalized_shape[0]):
+            # eager training step: forward and backward nodes both in C++
+            return fused_layernorm_cuda.layernorm_autograd(input, self.weight, self.bias, self.eps)
         if input.dim() == 2 and len(self.normalized_shape) == 1:
             # direct 2-D case: the reference's fast path (layernorm.py:176-180)
             return FusedLayerNormFunction.apply(input, self.normalized_shape, self.weight, self.bias, self.eps)

@@ -511,6 +511,29 @@ def test_kernel_families_agree_with_oracle(path_override, shape, dtype, kind, mo
     assert capi.lib().fln_device_status() == 0
 
 
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype,shape", [(BF16, (300, 12288)), (F32, (300, 12288)), (F16, (64, 20480)),
+                                         (BF16, (2100, 16384)), (F32, (33, 40960))])
+def test_long_rows_backward(shape, dtype, kind):
+    """Rows beyond 16 columns per thread of a 512-thread CTA: the vectorised pair of kernels,
+    with and without the incoming gradient."""
+    rows, cols = shape
+    x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 9, rows, cols, dtype, residual=True)
+    f = O.norm_forward(x, gamma, None if kind == "rmsnorm" else beta, None, kind)
+    for dres in (None, res):
+        got = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        want = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, dres, kind)
+        if dtype == F32:
+            torch.testing.assert_close(got["dx"], want["dx32"], rtol=1e-5, atol=1e-5)
+        else:
+            U.assert_out_close(got["dx"], want["dx"], dtype)
+        U.assert_param_grads_close(got["dgb_f32"][:cols], want["dgamma64"], want["abs64"][0], rows)
+        if kind == "layernorm":
+            U.assert_param_grads_close(got["dgb_f32"][cols:], want["dbeta64"], want["abs64"][1], rows)
+    only_params = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, want=(False, True, True))
+    U.assert_param_grads_close(only_params["dgb_f32"][:cols], want["dgamma64"], want["abs64"][0], rows)
+
+
 def test_pipelined_backward_adds_residual_gradient_in_place():
     """dx may be the buffer that holds the incoming residual-stream gradient."""
     rows, cols = 8192, 4096
@@ -528,6 +551,40 @@ def test_pipelined_backward_adds_residual_gradient_in_place():
     idx = torch.tensor([0, 17, 4095, 8191])
     want = O.norm_backward(dy[idx], x[idx], f["mean"][idx], f["rstd"][idx], gamma, res[idx])
     U.assert_out_close(sep[idx.cuda()].cpu(), want["dx"], BF16)
+    assert capi.lib().fln_device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype", [BF16, F32, F16])
+@pytest.mark.parametrize("shape", [(2048, 768), (1536, 1280), (1024, 2560), (640, 3072), (600, 5120), (304, 6144),
+                                   (300, 7168), (296, 12288), (2049, 768)])
+def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape, dtype, kind):
+    """Hidden sizes such as 768, 1280, 5120, 12288 divide evenly over the threads only with an
+    odd number of vectors per thread and, for some, shorter vectors; those plans exist in the
+    pipelined kernels.  (2049 rows: not a whole number of row groups, so the padded plan runs.)"""
+    path_override(2)
+    rows, cols = shape
+    x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 5, rows, cols, dtype, residual=True)
+    if kind == "rmsnorm":
+        beta = None
+    for r in (None, res):
+        got = U.run_forward(x, gamma, beta, r, kind)
+        want = O.norm_forward(x, gamma, beta, r, kind)
+        U.assert_out_close(got["y"], want["y"], dtype)
+        torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+        if r is not None:
+            assert torch.equal(got["sum"].view(torch.uint8), want["sum"].view(torch.uint8))
+    f = O.norm_forward(x, gamma, beta, None, kind)
+    for dres in (None, res):
+        gb = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        wb = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, dres, kind)
+        if dtype == F32:
+            torch.testing.assert_close(gb["dx"], wb["dx32"], rtol=1e-5, atol=1e-5)
+        else:
+            U.assert_out_close(gb["dx"], wb["dx"], dtype)
+        U.assert_param_grads_close(gb["dgb_f32"][:cols], wb["dgamma64"], wb["abs64"][0], rows)
+        if kind == "layernorm":
+            U.assert_param_grads_close(gb["dgb_f32"][cols:], wb["dbeta64"], wb["abs64"][1], rows)
     assert capi.lib().fln_device_status() == 0
 
 
