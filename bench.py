@@ -45,6 +45,7 @@ def parse():
     ap.add_argument("--rows", type=int, default=16384, help="rows per GPU")
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-chunk-rows", type=int, default=2048, help="rows per host<->device chunk of the e2e path")
     ap.add_argument("--cpu-sample-rows", type=int, default=2048)
     ap.add_argument("--sm-reserve", type=int, default=-1,
                     help="SMs the persistent kernels leave free (default: 0 on one GPU, 2 when an all-reduce overlaps)")
@@ -334,7 +335,7 @@ def run_ours(args):
     # ---- end to end: batch in pinned host memory, copies inside the timed region ----------
     e2e = None
     if not args.skip_e2e:
-        pipe = HostLayerNormFwdBwd(rows, cols, dt)
+        pipe = HostLayerNormFwdBwd(rows, cols, dt, chunk_rows=args.e2e_chunk_rows)
         xh, dyh = x.cpu().pin_memory(), dy.cpu().pin_memory()
         yh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
         dph = torch.empty(2 * cols, dtype=dt).pin_memory()

@@ -250,8 +250,9 @@ void fln_set_plan_override(int vecs_per_thread, int threads_per_row);
 /* Tuning hook: which kernel family serves aligned problems.  0 = automatic (the persistent
  * bulk-async pipeline once every CTA streams several tiles, register-resident kernels
  * otherwise), 1 = register-resident kernels only, 2 = the pipeline whenever the row fits,
- * 4 = like 2 but the backward uses the two-rows-per-barrier variant where the shape allows.
- * Query fln_backward_workspace_bytes again after changing it. */
+ * 3 = like 2 but dgamma / dbeta are reduced by a second kernel instead of in the tail of the
+ * backward launch, 4 = like 2 but the backward uses the two-rows-per-barrier variant where
+ * the shape allows.  Query fln_backward_workspace_bytes again after changing it. */
 void fln_set_path_override(int mode);
 
 /* Persistent kernels size their grids to fill every SM exactly and split the rows statically,
