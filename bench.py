@@ -244,33 +244,40 @@ def run_ours(args):
     # forward, backward (the column reduce is the tail of the same cooperative launch) (+ cast)
     launches_per_step = 2 + (1 if world > 1 else 0)
 
+    # N > 1: the all-reduce of the fp32 [dgamma | dbeta] partials and the rounding to bf16 run on
+    # a side stream, gated by an event behind the backward, so they overlap the next step and
+    # the main stream never waits for them (a training loop needs the parameter gradients only
+    # at its optimizer step).  Two buffers alternate; before a buffer is written again the main
+    # stream waits for the event that marks its previous reduction as finished, which by then
+    # lies a whole step in the past.  The last reductions are joined inside the timed region.
+    dgb2 = [dgb, torch.empty_like(dgb)]
+    side = torch.cuda.Stream() if world > 1 else None
+    ev_bwd = [torch.cuda.Event() for _ in range(2)]
+    ev_red = [torch.cuda.Event() for _ in range(2)]
+    step_no = [0]
+
     def fwd():
         capi.layernorm_forward(x, gamma, beta, y, mean, rstd, 1e-5)
-        if world > 1:
-            finish_pending()  # previous step's parameter gradients, overlapped with this forward
-
-    # N > 1: the all-reduce of the fp32 [dgamma | dbeta] partials is issued asynchronously and
-    # finished (wait + rounding to bf16) after the NEXT step's forward has been launched, so
-    # it overlaps that forward; two buffers alternate so a step never overwrites partials
-    # that are still being reduced.  The last step's reduction is finished inside the timed
-    # region.
-    dgb2 = [dgb, torch.empty_like(dgb)]
-    pending = []
 
     def finish_pending():
-        while pending:
-            work, buf = pending.pop(0)
-            work.wait()
-            capi.cast_from_f32(buf, dparams)
-
-    step_no = [0]
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(side)
 
     def bwd():
         if world > 1:
-            buf = dgb2[step_no[0] & 1]
+            k = step_no[0] & 1
+            buf = dgb2[k]
+            main = torch.cuda.current_stream()
+            if step_no[0] >= 2:
+                main.wait_event(ev_red[k])
             step_no[0] += 1
             capi.norm_backward(capi.LAYERNORM, dy, x, mean, rstd, gamma, None, dx, None, None, buf, ws)
-            pending.append((dist.all_reduce(buf, async_op=True), buf))
+            ev_bwd[k].record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ev_bwd[k])
+                dist.all_reduce(buf)
+                capi.cast_from_f32(buf, dparams, stream=side)
+                ev_red[k].record(side)
         else:
             capi.norm_backward(capi.LAYERNORM, dy, x, mean, rstd, gamma, None, dx, dparams[:cols], dparams[cols:],
                                None, ws)
