@@ -954,15 +954,22 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
     K = kk;
     tpr = t;
   }
-  if (K == 0) return P;
   // Row lengths 3, 5 or 7 times a power of two (768, 1280, 2560, 5120, 6144, 12288 ...) do not
   // divide over a power-of-two number of threads with a power-of-two number of 16-byte vectors
   // each; the padded plan above would run them through the bounds-checked kernel with a
   // quarter or more of the lanes idle.  Look for an exact fit with K in {3, 5, 7} and, if
   // need be, 8- or 4-byte vectors; the branch-free instantiation then applies.
   int vb = 16;
-  if (fK == 0 && rpt == 1 && (int64_t)K * tpr != nv) {
-    const int cap_elems = backward ? 16 : 32;
+  // Elements per thread the odd plans may use.  Backward, 16-bit types: 20 columns per thread
+  // (K = 5 vectors of 4) still compile without spills at 128 registers and run faster than
+  // the 16-column plans; 24 columns spill a little and are slower than 12 (6144 columns: 3986
+  // vs 5237 GB/s), but faster than the two-kernel long-row path (12288 columns: 4018 vs 3365
+  // GB/s), so they serve only rows that fit no other plan.  fp32 backward stays at 16.
+  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : 32, backward && elem_bytes == 2 ? 24 : 0};
+  for (int pass = 0; pass < 2; ++pass) {
+    const int cap_elems = caps[pass];
+    if (cap_elems == 0 || fK != 0 || rpt != 1) break;
+    if (pass == 0 ? !(K == 0 || (int64_t)K * tpr != nv) : K != 0) break;
     const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
     int best_elems = 0;
     for (int cvb = 16; cvb >= min_vb; cvb >>= 1) {
@@ -984,6 +991,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
       }
     }
   }
+  if (K == 0) return P;
   const int threads = tpr > cta_threads ? tpr : cta_threads;
   const int R = (threads / tpr) * rpt;
   const uint32_t row_bytes = (uint32_t)cols * elem_bytes;
@@ -1148,7 +1156,7 @@ static int launch_bwd_kernel(KernelT kern, const BwdParams& p, const PipePlan& P
 template <typename T, int KIND, int KK, int VB>
 static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = VB / (int)sizeof(T);
-  if constexpr (VEC >= 2 && KK * VEC <= 16) {
+  if constexpr (VEC >= 2 && KK * VEC <= (sizeof(T) == 2 ? 24 : 16)) {
     const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
     if (fuse && dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB>, p, P, st);
     if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB>, p, P, st);
