@@ -496,6 +496,13 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
 // *reduced tells whether dgamma / dbeta / dgb_f32 were produced by the launch itself (fused
 // column reduce); otherwise the caller reduces p.partials.
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);
+// the pipelined plan of a shape, for fln_describe_launch (returns false when the register or
+// generic kernels serve it)
+struct PipeDescription {
+  int vector_bytes, K, tpr, threads, rows_per_cta, stages;
+  int64_t grid;
+};
+bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out);
 // partial rows the pipelined backward writes for this shape (0 = not applicable)
 int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, bool with_dres);
 

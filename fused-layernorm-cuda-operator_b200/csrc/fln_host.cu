@@ -230,6 +230,22 @@ extern "C" int fln_describe_launch(int backward, int64_t rows, int64_t cols, int
   } else {
     out->grid = groups;
   }
+  out->pipelined = 0;
+  out->stages = 0;
+  out->vector_bytes = pl.vec * es;
+  PipeDescription pd;
+  if (aligned16 != 0 && rows > 0 && describe_pipeline(backward != 0, rows, (int)cols, es, &pd)) {
+    out->generic = 0;
+    out->pipelined = 1;
+    out->vec_elems = pd.vector_bytes / es;
+    out->vecs_per_thread = pd.K;
+    out->threads_per_row = pd.tpr;
+    out->threads_per_cta = pd.threads;
+    out->rows_per_cta = pd.rows_per_cta;
+    out->grid = pd.grid;
+    out->stages = pd.stages;
+    out->vector_bytes = pd.vector_bytes;
+  }
   return FLN_OK;
 }
 

@@ -1245,6 +1245,21 @@ static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres
   return plan_pipeline(true, rows, cols, es, 2, 1);
 }
 
+bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
+  PipePlan P = backward ? plan_bwd_pipeline(rows, cols, elem_bytes, false) : plan_pipeline(false, rows, cols, elem_bytes, 1);
+  if (!pipeline_wanted(P, rows)) return false;
+  // the odd plans exist only as branch-free instantiations; K = 8 only for fp32 forward
+  if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) && !P.full) return false;
+  out->vector_bytes = P.vb;
+  out->K = P.K;
+  out->tpr = P.g.tpr;
+  out->threads = P.threads;
+  out->rows_per_cta = P.g.R;
+  out->stages = P.g.S;
+  out->grid = P.grid;
+  return true;
+}
+
 int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, bool with_dres) {
   (void)kind;
   const int es = dtype == FLN_F32 ? 4 : 2;

@@ -37,7 +37,8 @@ STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 class LaunchInfo(C.Structure):
     _fields_ = [("generic", C.c_int), ("vec_elems", C.c_int), ("vecs_per_thread", C.c_int),
                 ("threads_per_row", C.c_int), ("threads_per_cta", C.c_int), ("rows_per_cta", C.c_int),
-                ("grid", C.c_int64), ("sm_count", C.c_int)]
+                ("grid", C.c_int64), ("sm_count", C.c_int), ("pipelined", C.c_int), ("stages", C.c_int),
+                ("vector_bytes", C.c_int)]
 
 
 _lib = None

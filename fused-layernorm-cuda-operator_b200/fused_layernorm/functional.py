@@ -47,7 +47,8 @@ def get_optimal_config(batch_size: int, hidden_size: int, dtype: torch.dtype = t
     return {
         "use_mixed_precision": dtype in (torch.float16, torch.bfloat16),
         "threads_per_block": fwd["threads_per_cta"],
-        "enable_persistent_kernel": bool(bwd["grid"] < max(1, (batch_size + bwd["rows_per_cta"] - 1) // bwd["rows_per_cta"])),
+        "enable_persistent_kernel": bool(fwd["pipelined"] or bwd["pipelined"] or bwd["grid"] < max(
+            1, (batch_size + bwd["rows_per_cta"] - 1) // bwd["rows_per_cta"])),
         "use_vectorized_load": fwd["vec_elems"] > 1,
         "use_tensor_cores": False,  # the path is memory-bound; tensor cores are not used
         "forward": fwd,

@@ -238,6 +238,10 @@ typedef struct {
   int rows_per_cta;
   int64_t grid;      /* CTAs launched                                                     */
   int sm_count;
+  int pipelined;     /* 1: the persistent bulk-async (TMA) pipeline serves this shape; the  */
+                     /* fields above then describe its plan                                */
+  int stages;        /* shared-memory stages of that pipeline (0 otherwise)                */
+  int vector_bytes;  /* bytes per vector access: 16, or 8 / 4 in the odd-K plans           */
 } fln_launch_info;
 int fln_describe_launch(int backward, int64_t rows, int64_t cols, int dtype, int aligned16,
                         fln_launch_info* out);

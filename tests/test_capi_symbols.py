@@ -51,6 +51,14 @@ def test_host_only_entry_points():
 def test_launch_planner_without_a_device():
     info = capi.describe_launch(False, 16384, 8192, torch.bfloat16)
     assert info["generic"] == 0 and info["vec_elems"] == 8 and info["threads_per_row"] * info["vecs_per_thread"] == 1024
+    assert info["pipelined"] == 1 and info["stages"] >= 2 and info["vector_bytes"] == 16
+    # 5120 = 5 * 1024: backward gives every thread 5 vectors of 4 columns, forward 5 of 4 elements
+    b5 = capi.describe_launch(True, 16384, 5120, torch.bfloat16)
+    assert b5["pipelined"] == 1 and b5["vecs_per_thread"] == 5 and b5["vector_bytes"] == 8 and b5["threads_per_row"] == 256
+    f3 = capi.describe_launch(False, 16384, 768, torch.bfloat16)
+    assert f3["pipelined"] == 1 and f3["vecs_per_thread"] == 3 and f3["threads_per_row"] == 32
+    small = capi.describe_launch(False, 32, 4096, torch.bfloat16)
+    assert small["pipelined"] == 0
     odd = capi.describe_launch(False, 17, 1023, torch.bfloat16)
     assert odd["vec_elems"] == 1 and odd["generic"] == 0
     huge = capi.describe_launch(False, 1, 100000, torch.float32)
