@@ -7,6 +7,7 @@
               kernel (two launches), 32768 x 8192 bf16
   c4_delayed  the same output in one pass with a caller-supplied scale (delayed scaling)
   c4_rowwise  the same output in one pass with one scale per row
+  c4_mxfp8    the same in one pass as MXFP8 (one E8M0 scale byte per 32 elements)
   dres        LayerNorm backward with incoming residual-stream gradient, 16384 x 8192 bf16
 
 CUDA events around back-to-back launches after warm-up; every tensor is larger than the
@@ -77,6 +78,9 @@ def c4(args, mode):
         fn = lambda: capi.norm_forward_fp8(capi.RMSNORM, x, r, g, None, q, s, None, rstd, amax, scale, 1e-6)
     elif mode == "delayed":
         fn = lambda: capi.norm_forward_fp8_delayed(capi.RMSNORM, x, r, g, None, q, s, None, None, scale, amax, 1e-6)
+    elif mode == "mxfp8":
+        bs = torch.empty(rows, cols // 32, dtype=torch.uint8, device="cuda")
+        fn = lambda: capi.norm_forward_mxfp8(capi.RMSNORM, x, r, g, None, q, bs, s, None, None, None, 1e-6)
     else:
         fn = lambda: capi.norm_forward_fp8_rowwise(capi.RMSNORM, x, r, g, None, q, s, None, rstd, rs, None, 1e-6)
     t = loop_us(fn, args.warmup, args.iters)
@@ -99,7 +103,7 @@ def dres(args):
 CONFIGS = {
     "c3": lambda a: c3(a, False), "c3_dres": lambda a: c3(a, True),
     "c4": lambda a: c4(a, "two_phase"), "c4_delayed": lambda a: c4(a, "delayed"),
-    "c4_rowwise": lambda a: c4(a, "rowwise"), "dres": dres,
+    "c4_rowwise": lambda a: c4(a, "rowwise"), "c4_mxfp8": lambda a: c4(a, "mxfp8"), "dres": dres,
 }
 
 

@@ -16,6 +16,12 @@
 //   per-row scaling  every row gets its own scale 448 / max|y_row|, known once the row is
 //                    in registers, and the scales are returned as an fp32 vector.
 // Both are norm_amax_kernel with QMODE 1 / 2: same loads, same statistics, then the codes.
+//   block scaling    (QMODE 3) the OCP microscaling form MXFP8 that Blackwell's block-scaled
+//                    tensor-core instructions consume: every 32 consecutive elements of a row
+//                    share one power-of-two scale, stored as an E8M0 byte, chosen as
+//                    2^(floor(log2(block max)) - 8); the elements are e4m3.  The 32 elements
+//                    sit in 4 (16-bit input) or 8 (fp32) neighbouring lanes, so the block
+//                    maximum is two or three shuffles; one pass, 7 + 1/32 bytes per element.
 //
 // Both kernels follow the register-resident forward (fln_forward.cu): the row lives in
 // registers as floats, statistics are the shifted two-pass form with sum reductions, 16-bit
@@ -38,6 +44,7 @@ struct Fp8Params {
   float* scale;
   const float* scale_in;  // QMODE 1: one fp32, read by every CTA
   float* row_scale;       // QMODE 2: [rows] fp32, written
+  unsigned char* block_scale;  // QMODE 3: [rows, cols / 32] E8M0 bytes, written
   int64_t rows;
   int cols;
   int nv;
@@ -125,7 +132,8 @@ __device__ __forceinline__ float row_max(float m, int tpr, float* smem) {
   return m;
 }
 
-// QMODE 0: phase 1 of the two-launch form (amax only); 1: quantize with *scale_in; 2: per-row scale
+// QMODE 0: phase 1 of the two-launch form (amax only); 1: quantize with *scale_in; 2: per-row
+// scale; 3: one E8M0 scale per block of 32 elements (MXFP8)
 template <typename TI, int VEC, int K, int KIND, bool FULL, int QMODE>
 __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(const Fp8Params p) {
   __shared__ __align__(16) float s_red[2][32];
@@ -236,7 +244,7 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (FULL || (row_ok && iv < p.nv)) {
+    if (QMODE != 3 && (FULL || (row_ok && iv < p.nv))) {
       float o[VEC];
       affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
@@ -247,6 +255,38 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
         Pack<unsigned char, VEC> out;
         pack_fp8<VEC>(o, out);
         st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
+      }
+    }
+  }
+  if (QMODE == 3) {
+    constexpr int G = 32 / VEC;  // neighbouring lanes that hold one block of 32 elements
+    unsigned char* __restrict__ bs = p.block_scale + (row_ok ? row : 0) * (int64_t)(p.cols / 32);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      const bool act = FULL || (row_ok && iv < p.nv);
+      float o[VEC];
+      float bm = 0.f;
+      if (act) {
+        affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) bm = fmaxf(bm, fabsf(o[i]));
+      }
+      amax = fmaxf(amax, bm);
+      // cols % 32 == 0, so the G lanes of a block are all active or all idle; every lane
+      // takes part in the shuffles
+#pragma unroll
+      for (int off = 1; off < G; off <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, off));
+      const unsigned int ef = (__float_as_uint(bm) >> 23) & 0xffu;  // biased exponent of the block maximum
+      const unsigned int e8 = ef > 8u ? ef - 8u : 0u;               // the scale is 2^(e8 - 127)
+      const float inv = __uint_as_float((254u - e8) << 23);         // 2^(127 - e8), exact
+      if (act) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] *= inv;
+        Pack<unsigned char, VEC> out;
+        pack_fp8<VEC>(o, out);
+        st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
+        if ((lane_r & (G - 1)) == 0) bs[iv / G] = (unsigned char)e8;
       }
     }
   }
@@ -329,6 +369,7 @@ static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
   p.nv = p.cols / VFULL;
   const unsigned grid = (unsigned)((p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta);
   const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
+  if (qmode == 3 && (p.cols % 32 != 0 || pl.tpr < 32 / VFULL)) return FLN_ERR_UNSUPPORTED;
   if (p.amax != nullptr && cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
 #define FLN_FP8_LAUNCH(KK, FF)                                                                  \
   if (qmode == 0) {                                                                             \
@@ -336,6 +377,8 @@ static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
     norm_quant_kernel<TI, VFULL, KK, KIND, FF><<<grid, pl.threads, 0, st>>>(p);                 \
   } else if (qmode == 1) {                                                                      \
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 1><<<grid, pl.threads, 0, st>>>(p);               \
+  } else if (qmode == 3) {                                                                      \
+    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 3><<<grid, pl.threads, 0, st>>>(p);               \
   } else {                                                                                      \
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 2><<<grid, pl.threads, 0, st>>>(p);               \
   }
@@ -368,13 +411,14 @@ using namespace fln;
 static int fp8_entry(int qmode, int kind, const void* x, const void* residual, const void* gamma,
                      const void* beta, void* q, void* sum_out, float* mean, float* rstd, float* amax,
                      float* scale, const float* scale_in, float* row_scale, int64_t rows, int64_t cols,
-                     int io_dtype, float eps, void* stream) {
+                     int io_dtype, float eps, void* stream, unsigned char* block_scale = nullptr) {
   if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
   if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
   if (qmode == 0 && (amax == nullptr || scale == nullptr)) return FLN_ERR_NULL;
   if (qmode == 1 && scale_in == nullptr) return FLN_ERR_NULL;
   if (qmode == 2 && row_scale == nullptr) return FLN_ERR_NULL;
+  if (qmode == 3 && block_scale == nullptr) return FLN_ERR_NULL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (rows == 0) {
     // empty tensor: amax = 0, scale = 1
@@ -409,6 +453,7 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
   p.scale = scale;
   p.scale_in = scale_in;
   p.row_scale = row_scale;
+  p.block_scale = block_scale;
   p.rows = rows;
   p.cols = (int)cols;
   p.nv = 0;
@@ -448,4 +493,12 @@ extern "C" int fln_norm_forward_fp8_rowwise(int kind, const void* x, const void*
                                             void* stream) {
   return fp8_entry(2, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, nullptr,
                    row_scale, rows, cols, io_dtype, eps, stream);
+}
+
+extern "C" int fln_norm_forward_mxfp8(int kind, const void* x, const void* residual, const void* gamma,
+                                      const void* beta, void* q, unsigned char* block_scale, void* sum_out,
+                                      float* mean, float* rstd, float* amax_out, int64_t rows, int64_t cols,
+                                      int io_dtype, float eps, void* stream) {
+  return fp8_entry(3, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, nullptr, nullptr,
+                   rows, cols, io_dtype, eps, stream, block_scale);
 }

@@ -248,6 +248,38 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_fp8_scaled(int64_t kind, const T
   return {q, sum, row_scale, amax};
 }
 
+// One-pass MXFP8 output: (q e4m3, sum, E8M0 scale bytes [rows, cols / 32] as uint8, amax)
+std::tuple<Tensor, Tensor, Tensor, Tensor> norm_mxfp8(int64_t kind, const Tensor& input, const OptTensor& residual,
+                                                      const OptTensor& gamma, const OptTensor& beta, double epsilon) {
+  TORCH_CHECK(kind == FLN_LAYERNORM || kind == FLN_RMSNORM, "kind must be 0 (layernorm) or 1 (rmsnorm)");
+  Tensor x = check_matrix(input, "input");
+  TORCH_CHECK(x.size(1) % 32 == 0, "mxfp8 output needs a row length that is a multiple of 32");
+  const int dt = dtype_code(x, "norm_mxfp8");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor gk, bk, rk, sum;
+  const void* g = param_ptr(gamma, x, "Gamma", gk);
+  const void* b = param_ptr(beta, x, "Beta", bk);
+  TORCH_CHECK(!(kind == FLN_RMSNORM && b != nullptr), "rmsnorm takes no beta");
+  const void* r = nullptr;
+  void* s = nullptr;
+  if (residual.has_value() && residual->defined()) {
+    rk = check_like(*residual, x, "residual");
+    r = rk.data_ptr();
+    sum = at::empty_like(x);
+    s = sum.data_ptr();
+  } else {
+    sum = at::empty({0}, x.options());
+  }
+  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor scales = at::empty({x.size(0), x.size(1) / 32}, x.options().dtype(at::kByte));
+  Tensor amax = at::empty({1}, x.options().dtype(at::kFloat));
+  check_status(fln_norm_forward_mxfp8((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), scales.data_ptr<uint8_t>(), s,
+                                      nullptr, nullptr, amax.data_ptr<float>(), x.size(0), x.size(1), dt,
+                                      (float)epsilon, stream_of(x)),
+               "norm_mxfp8");
+  return {q, sum, scales, amax};
+}
+
 // ---------------------------------------------------------------------------------------
 // backward family
 // ---------------------------------------------------------------------------------------
@@ -403,6 +435,7 @@ TORCH_LIBRARY(fused_layernorm, m) {
   m.def("add_rmsnorm_fwd(Tensor input, Tensor residual, Tensor? gamma, float epsilon) -> (Tensor, Tensor, Tensor)");
   m.def("norm_fp8(int kind, Tensor input, Tensor? residual, Tensor? gamma, Tensor? beta, float epsilon) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("norm_fp8_scaled(int kind, Tensor input, Tensor? residual, Tensor? gamma, Tensor? beta, Tensor? scale_in, float epsilon) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.def("norm_mxfp8(int kind, Tensor input, Tensor? residual, Tensor? gamma, Tensor? beta, float epsilon) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("layernorm_bwd(Tensor grad_output, Tensor input, Tensor mean, Tensor rstd, Tensor? gamma, Tensor? dres_in, bool need_dx, bool need_dgamma, bool need_dbeta) -> (Tensor, Tensor, Tensor)");
   m.def("rmsnorm_bwd(Tensor grad_output, Tensor input, Tensor rstd, Tensor? gamma, Tensor? dres_in, bool need_dx, bool need_dgamma) -> (Tensor, Tensor)");
   m.def("layernorm_bwd_f32(Tensor grad_output, Tensor input, Tensor mean, Tensor rstd, Tensor? gamma) -> (Tensor, Tensor)");
@@ -418,6 +451,7 @@ TORCH_LIBRARY_IMPL(fused_layernorm, CUDA, m) {
   m.impl("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.impl("norm_fp8", &norm_fp8);
   m.impl("norm_fp8_scaled", &norm_fp8_scaled);
+  m.impl("norm_mxfp8", &norm_mxfp8);
   m.impl("layernorm_bwd", &layernorm_bwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
   m.impl("layernorm_bwd_f32", &layernorm_bwd_f32);
@@ -503,6 +537,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       "(q fp8-e4m3, residual sum, scale = 448 / amax)", py::arg("input"), py::arg("residual") = py::none(),
       py::arg("gamma") = py::none(), py::arg("epsilon") = 1e-6);
+  m.def("norm_mxfp8", &norm_mxfp8, py::arg("kind"), py::arg("input"), py::arg("residual") = py::none(),
+        py::arg("gamma") = py::none(), py::arg("beta") = py::none(), py::arg("epsilon") = 1e-5);
   m.def("norm_fp8_scaled", &norm_fp8_scaled, py::arg("kind"), py::arg("input"), py::arg("residual") = py::none(),
         py::arg("gamma") = py::none(), py::arg("beta") = py::none(), py::arg("scale_in") = py::none(),
         py::arg("epsilon") = 1e-5);

@@ -29,7 +29,7 @@ SYMBOLS = [
     "fln_graph_begin", "fln_graph_stream", "fln_graph_end", "fln_graph_launch", "fln_graph_destroy",
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
-    "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise",
+    "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -65,6 +65,7 @@ def lib() -> C.CDLL:
     L.fln_norm_forward_fp8.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_norm_forward_fp8_delayed.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_norm_forward_fp8_rowwise.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
+    L.fln_norm_forward_mxfp8.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_backward_workspace_bytes.restype = sz
     L.fln_backward_workspace_bytes.argtypes = [i64, i64, i32]
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
@@ -163,6 +164,16 @@ def norm_forward_fp8_rowwise(kind, x, residual, gamma, beta, q, sum_out, mean, r
                                              ptr(sum_out), ptr(mean), ptr(rstd), ptr(row_scale), ptr(amax_out),
                                              rows, cols, dtype_code(x), eps, stream_handle(stream)),
           "fln_norm_forward_fp8_rowwise")
+
+
+def norm_forward_mxfp8(kind, x, residual, gamma, beta, q, block_scale, sum_out, mean, rstd, amax_out, eps,
+                       stream=None):
+    """One launch: MXFP8 output, one E8M0 scale byte per 32 consecutive elements of a row
+    (block_scale: uint8 [rows, cols // 32]); q = sat_e4m3(y / 2^(byte - 127))."""
+    rows, cols = x.shape
+    check(lib().fln_norm_forward_mxfp8(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q), ptr(block_scale),
+                                       ptr(sum_out), ptr(mean), ptr(rstd), ptr(amax_out), rows, cols, dtype_code(x),
+                                       eps, stream_handle(stream)), "fln_norm_forward_mxfp8")
 
 
 def backward_workspace_bytes(rows, cols, dtype) -> int:

@@ -74,6 +74,14 @@ def _(kind, input, residual, gamma, beta, scale_in, epsilon):
     return q, s, row_scale, input.new_empty((1,), dtype=torch.float32)
 
 
+@torch.library.register_fake("fused_layernorm::norm_mxfp8")
+def _(kind, input, residual, gamma, beta, epsilon):
+    q = input.new_empty(input.shape, dtype=torch.float8_e4m3fn)
+    s = torch.empty_like(input, memory_format=torch.contiguous_format) if residual is not None else input.new_empty((0,))
+    scales = input.new_empty((input.shape[0], input.shape[1] // 32), dtype=torch.uint8)
+    return q, s, scales, input.new_empty((1,), dtype=torch.float32)
+
+
 @torch.library.register_fake("fused_layernorm::layernorm_bwd")
 def _(grad_output, input, mean, rstd, gamma, dres_in, need_dx, need_dgamma, need_dbeta):
     cols = input.shape[1]

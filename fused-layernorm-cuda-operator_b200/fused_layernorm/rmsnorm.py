@@ -98,6 +98,24 @@ def fused_add_norm_fp8_rowwise(input: torch.Tensor, residual: Optional[torch.Ten
     return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), rs
 
 
+def fused_add_norm_mxfp8(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                         weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                         eps: float = 1e-6, kind: str = "rmsnorm"):
+    """(q, sum, block_scale) in ONE pass, in the OCP microscaling format MXFP8 that Blackwell's
+    block-scaled matrix instructions take: q is float8_e4m3fn, and every 32 consecutive elements
+    of the last dimension share one power-of-two scale, returned as E8M0 bytes of shape
+    input.shape[:-1] + (hidden // 32,) (dtype float8_e8m0fnu where torch has it, else uint8).
+    Dequantize with q.float() * 2 ** (byte - 127) per block.  Forward only."""
+    _require_cuda(input)
+    k = _ops.RMSNORM if kind == "rmsnorm" else _ops.LAYERNORM
+    q, s, scales, _amax = _t.norm_mxfp8(k, _flat(input), None if residual is None else _flat(residual), weight, bias,
+                                        eps)
+    scales = scales.reshape(*input.shape[:-1], input.shape[-1] // 32)
+    if hasattr(torch, "float8_e8m0fnu"):
+        scales = scales.view(torch.float8_e8m0fnu)
+    return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), scales
+
+
 class FusedRMSNorm(nn.Module):
     """torch.nn.RMSNorm-compatible module (normalized_shape, eps, elementwise_affine; parameter `weight`)."""
 

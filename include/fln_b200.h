@@ -135,6 +135,19 @@ int fln_norm_forward_fp8_rowwise(int kind, const void* x, const void* residual, 
                                  float* row_scale, float* amax_out, int64_t rows, int64_t cols,
                                  int io_dtype, float eps, void* stream);
 
+/* One-pass MXFP8 output (OCP microscaling, the block-scaled form Blackwell's tensor cores
+ * consume): every 32 consecutive elements of a row share a power-of-two scale
+ * 2^(floor(log2(max|y| over the block)) - 8), stored as an E8M0 byte (value 2^(byte - 127); an
+ * all-zero block stores 0); q = sat_e4m3(y / scale).
+ *   q            [rows, cols] bytes (e4m3 codes)
+ *   block_scale  [rows, cols / 32] bytes (E8M0), required; cols must be a multiple of 32
+ *   amax_out     one fp32 or NULL: max|y| over the whole tensor
+ * Otherwise as fln_norm_forward_fp8_rowwise.  No counterpart in the reference. */
+int fln_norm_forward_mxfp8(int kind, const void* x, const void* residual, const void* gamma,
+                           const void* beta, void* q, unsigned char* block_scale, void* sum_out,
+                           float* mean, float* rstd, float* amax_out, int64_t rows, int64_t cols,
+                           int io_dtype, float eps, void* stream);
+
 /* ----------------------------------------------------------------------------------
  * Backward
  * -------------------------------------------------------------------------------- */

@@ -144,6 +144,24 @@ def quant_fp8_rowwise(y32):
     return q, scale, rmax.max().reshape(1) if rmax.numel() else torch.zeros(1)
 
 
+def quant_mxfp8(y32, e8m0=None):
+    """OCP microscaling MXFP8: blocks of 32 consecutive elements of a row share the scale
+    2^(floor(log2(block max)) - 8), stored as the E8M0 byte floor(log2(max)) - 8 + 127 (0 for a
+    block whose maximum is below 2^-119, zero included); elements are saturating e4m3 codes of
+    y / scale.  Returns (codes uint8 [rows, cols], scale bytes uint8 [rows, cols // 32]).  With
+    `e8m0` given, those scale bytes are used instead of being derived."""
+    y32 = _c(y32).float()
+    rows, cols = y32.shape
+    blocks = y32.reshape(rows, cols // 32, 32)
+    if e8m0 is None:
+        amax = blocks.abs().amax(dim=-1)
+        expf = (amax.view(torch.int32) >> 23) & 0xFF          # biased exponent = floor(log2) + 127
+        e8m0 = torch.clamp(expf - 8, min=0).to(torch.uint8)
+    inv = torch.pow(2.0, 127.0 - e8m0.to(torch.float64)).to(torch.float32)  # exact powers of two
+    q = e4m3_encode((blocks * inv[..., None]).reshape(rows, cols))
+    return q, e8m0
+
+
 def ref_g2_layernorm(x, gamma, beta, eps=1e-5, gelu=False):
     """Literal fp32 restatement of the reference's shipped kernel, summation order included."""
     x = _c(x).float()

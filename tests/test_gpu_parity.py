@@ -317,6 +317,41 @@ def test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residu
     torch.testing.assert_close(rstd.cpu(), want["rstd"], rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
+@pytest.mark.parametrize("dtype", [BF16, F16, F32])
+@pytest.mark.parametrize("shape", [(64, 8192), (257, 1024), (5, 4096), (33, 96)])
+def test_mxfp8_block_scaled_output(shape, dtype, kind, residual):
+    rows, cols = shape
+    x, gamma, beta, _, res = U.make_inputs(20247, rows, cols, dtype, residual=residual, outliers=True)
+    if kind == "rmsnorm":
+        beta = None
+    want = O.norm_forward(x, gamma, beta, res, kind, 1e-6)
+    y32 = want["y32"]
+    q = U.Guarded((rows, cols), torch.uint8)
+    bs = U.Guarded((rows, cols // 32), torch.uint8)
+    s = U.Guarded((rows, cols), dtype) if residual else None
+    amax = torch.full((1,), -1.0, device="cuda")
+    capi.norm_forward_mxfp8(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t, bs.t,
+                            s.t if s else None, None, None, amax, 1e-6)
+    torch.cuda.synchronize()
+    got_e = bs.check().cpu()
+    _, want_e = O.quant_mxfp8(y32)
+    # the scale byte is an exponent: it may differ by one only where the block maximum sits
+    # within rounding of a power of two
+    de = (got_e.to(torch.int32) - want_e.to(torch.int32)).abs()
+    assert int(de.max()) <= 1
+    bmax = y32.reshape(rows, cols // 32, 32).abs().amax(-1)
+    frac = torch.frexp(bmax)[0]
+    assert bool((((frac - 0.5).abs() < 1e-5) | ((frac - 1.0).abs() < 1e-5))[de > 0].all())
+    # codes against the quantizer run with the device's own scale bytes
+    wq, _ = O.quant_mxfp8(y32, got_e)
+    d = O.fp8_code_distance(q.check().cpu(), wq)
+    assert int(d.max()) <= 1 and int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+    torch.testing.assert_close(amax.cpu(), y32.abs().max().reshape(1), rtol=1e-5, atol=0)
+    if residual:
+        assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
+
+
 def test_fp8_rejects_ragged_rows():
     x = torch.randn(4, 1023, device="cuda", dtype=BF16)
     q = torch.empty(4, 1023, dtype=torch.uint8, device="cuda")

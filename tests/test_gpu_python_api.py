@@ -290,6 +290,25 @@ def test_fp8_one_pass_functions():
     assert s3 is None and rs3.shape == (256,)
 
 
+def test_mxfp8_function_dequantizes_to_the_normalized_values():
+    from fused_layernorm import fused_add_norm_mxfp8
+    x = torch.randn(4, 64, 2048, device="cuda", dtype=BF16) * 3
+    r = (0.5 * torch.randn(4, 64, 2048, device="cuda")).to(BF16)
+    w = (1 + 0.1 * torch.randn(2048, device="cuda")).to(BF16)
+    q, s, scales = fused_add_norm_mxfp8(x, r, w)
+    assert q.shape == x.shape and q.dtype == torch.float8_e4m3fn and scales.shape == (4, 64, 64)
+    assert torch.equal(s, x + r)
+    want = O.norm_forward(x.cpu().reshape(-1, 2048), w.cpu(), None, r.cpu().reshape(-1, 2048), "rmsnorm", 1e-6)["y32"]
+    e = scales.view(torch.uint8).cpu().reshape(-1, 64).to(torch.float64)
+    deq = (q.float().cpu().reshape(-1, 64, 32).double() * torch.pow(2.0, e - 127)[..., None]).reshape(-1, 2048)
+    # e4m3 keeps 3 mantissa bits and the block maximum is scaled into [256, 512): the error is at
+    # most half a step of the element's binade, and one step (32 * scale) where it saturates
+    step = torch.pow(2.0, e - 127)[..., None].expand(-1, -1, 32).reshape(-1, 2048)
+    err = (deq - want.double()).abs()
+    assert bool((err <= want.abs().double() * 0.0625 + 64 * step).all())
+    assert float((err / (want.abs().double() + 1e-3)).median()) < 0.04
+
+
 def test_replace_layernorm_modules_on_device():
     model = nn.Sequential(nn.Linear(256, 256), nn.LayerNorm(256), nn.GELU(), nn.LayerNorm(256)).cuda()
     x = torch.randn(16, 256, device="cuda")

@@ -116,7 +116,7 @@ def test_replace_layernorm_modules_shares_parameters():
 def test_operator_schemas_and_fake_tracing():
     ops = torch.ops.fused_layernorm
     for name in ["layernorm", "layernorm_gelu", "layernorm_fwd", "rmsnorm_fwd", "add_layernorm_fwd", "add_rmsnorm_fwd",
-                 "norm_fp8", "norm_fp8_scaled", "layernorm_bwd", "rmsnorm_bwd", "layernorm_bwd_f32", "cast_from_f32"]:
+                 "norm_fp8", "norm_fp8_scaled", "norm_mxfp8", "layernorm_bwd", "rmsnorm_bwd", "layernorm_bwd_f32", "cast_from_f32"]:
         assert hasattr(ops, name)
     assert "Tensor? gamma" in str(ops.layernorm_fwd.default._schema)
     # shape propagation through the fake implementations (what torch.compile relies on)
@@ -135,6 +135,8 @@ def test_operator_schemas_and_fake_tracing():
     assert q.dtype == torch.float8_e4m3fn and s8.shape == (6, 32) and rs.numel() == 0 and amax.shape == (1,)
     q, s8, rs, amax = ops.norm_fp8_scaled(1, x, None, w, None, None, 1e-6)
     assert rs.shape == (6,) and rs.dtype == torch.float32 and s8.numel() == 0
+    q, s8, bsc, amax = ops.norm_mxfp8(1, x, x, w, None, 1e-6)
+    assert q.dtype == torch.float8_e4m3fn and bsc.shape == (6, 1) and bsc.dtype == torch.uint8
     dxf, dgb = ops.layernorm_bwd_f32(y, x, mean, rstd, w)
     assert dgb.shape == (64,) and dgb.dtype == torch.float32
 

@@ -137,3 +137,27 @@ def test_scaled_fp8_quantizers_match_torch_cast():
     want = (y * scale[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
     assert torch.equal(q, want)
     assert float(scale[3]) == 1.0 and int(q[3].max()) == 0
+
+
+def test_mxfp8_quantizer_matches_torch_composition():
+    """Block-scaled quantizer against the same thing spelled with torch primitives
+    (frexp for floor(log2), the float8 casts for the codes and the E8M0 byte)."""
+    g = torch.Generator().manual_seed(78)
+    y = torch.randn(9, 256, generator=g) * torch.logspace(-3, 3, 9)[:, None]
+    y[2, 32:64] = 0
+    y[4, 5] = 3e4
+    q, e8 = O.quant_mxfp8(y)
+    blocks = y.reshape(9, 8, 32)
+    amax = blocks.abs().amax(-1)
+    _, ex = torch.frexp(amax)                      # amax = m * 2^ex, m in [0.5, 1)
+    want_e = torch.where(amax > 0, ex - 1 - 8 + 127, torch.zeros_like(ex)).clamp(min=0)
+    assert torch.equal(e8.to(torch.int32), want_e.to(torch.int32))
+    scale = torch.pow(2.0, want_e.double() - 127).float()
+    if hasattr(torch, "float8_e8m0fnu"):
+        assert torch.equal(scale[amax > 0].to(torch.float8_e8m0fnu).view(torch.uint8), e8[amax > 0])
+    want_q = (blocks / scale[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).reshape(9, 256)
+    assert torch.equal(q, want_q)
+    assert int(q[2, 32:64].max()) == 0 and int(e8[2, 1]) == 0
+    # the largest element of every block lands in [256, 512) before saturation: top binade
+    top = (blocks / scale[..., None]).abs().amax(-1)[amax > 0]
+    assert bool(((top >= 256) & (top < 512)).all())
