@@ -393,7 +393,9 @@ struct LayerNormAutograd : public torch::autograd::Function<LayerNormAutograd> {
     const bool has_g = gamma.has_value() && gamma->defined();
     const bool has_b = beta.has_value() && beta->defined();
     ctx->save_for_backward({input, has_g ? *gamma : Tensor(), std::get<1>(t), std::get<2>(t)});
-    ctx->saved_data["has_b"] = has_b;
+    // needs_input_grad counts only the tensor arguments that are present
+    ctx->saved_data["i_g"] = has_g ? (int64_t)1 : (int64_t)-1;
+    ctx->saved_data["i_b"] = has_b ? (int64_t)(has_g ? 2 : 1) : (int64_t)-1;
     return std::get<0>(t);
   }
   static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
@@ -401,10 +403,10 @@ struct LayerNormAutograd : public torch::autograd::Function<LayerNormAutograd> {
     auto saved = ctx->get_saved_variables();
     const Tensor& input = saved[0];
     const Tensor& gamma = saved[1];
-    const bool has_b = ctx->saved_data["has_b"].toBool();
+    const int64_t i_g = ctx->saved_data["i_g"].toInt(), i_b = ctx->saved_data["i_b"].toInt();
     const bool need_dx = ctx->needs_input_grad(0);
-    const bool need_dg = gamma.defined() && ctx->needs_input_grad(1);
-    const bool need_db = has_b && ctx->needs_input_grad(2);
+    const bool need_dg = i_g >= 0 && ctx->needs_input_grad((size_t)i_g);
+    const bool need_db = i_b >= 0 && ctx->needs_input_grad((size_t)i_b);
     BwdOut o = norm_backward(FLN_LAYERNORM, grad_outputs[0], input, saved[2], saved[3],
                              gamma.defined() ? OptTensor(gamma) : std::nullopt, std::nullopt, need_dx, need_dg, need_db,
                              false, "layernorm_backward");
@@ -413,6 +415,59 @@ struct LayerNormAutograd : public torch::autograd::Function<LayerNormAutograd> {
 };
 Tensor layernorm_autograd(const Tensor& input, const OptTensor& gamma, const OptTensor& beta, double epsilon) {
   return LayerNormAutograd::apply(input, gamma, beta, epsilon);
+}
+
+// The same for RMSNorm and for the fused residual-add forms: outputs (y, sum); sum is an empty
+// tensor without a residual.  The gradient that arrives for `sum` (the residual stream of a
+// pre-norm block) goes into the backward kernel as its incoming residual gradient, and the one
+// dx that comes out is the gradient of both `input` and `residual`.
+struct NormAutograd : public torch::autograd::Function<NormAutograd> {
+  static torch::autograd::tensor_list forward(torch::autograd::AutogradContext* ctx, int64_t kind, const Tensor& input,
+                                              const OptTensor& residual, const OptTensor& gamma, const OptTensor& beta,
+                                              double epsilon) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    TORCH_CHECK(kind == FLN_LAYERNORM || kind == FLN_RMSNORM, "kind must be 0 (layernorm) or 1 (rmsnorm)");
+    TORCH_CHECK(!(kind == FLN_RMSNORM && beta.has_value() && beta->defined()), "rmsnorm takes no beta");
+    const bool has_r = residual.has_value() && residual->defined();
+    FwdOut o = norm_forward((int)kind, input, residual, gamma, beta, epsilon, FLN_ACT_NONE, true,
+                            kind == FLN_LAYERNORM ? "add_layernorm" : "add_rmsnorm");
+    const bool has_g = gamma.has_value() && gamma->defined();
+    const bool has_b = beta.has_value() && beta->defined();
+    // the normalized tensor is the sum when there is a residual
+    ctx->save_for_backward({has_r ? o.sum : input, has_g ? *gamma : Tensor(),
+                            kind == FLN_LAYERNORM ? o.mean : Tensor(), o.rstd});
+    ctx->saved_data["kind"] = kind;
+    ctx->saved_data["has_r"] = has_r;
+    // needs_input_grad counts only the tensor arguments that are present
+    int64_t next = 1;
+    ctx->saved_data["i_res"] = has_r ? next++ : (int64_t)-1;
+    ctx->saved_data["i_g"] = has_g ? next++ : (int64_t)-1;
+    ctx->saved_data["i_b"] = has_b ? next++ : (int64_t)-1;
+    return {o.y, has_r ? o.sum : at::empty({0}, input.options())};
+  }
+  static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                               torch::autograd::tensor_list grads) {
+    auto saved = ctx->get_saved_variables();
+    const int kind = (int)ctx->saved_data["kind"].toInt();
+    const bool has_r = ctx->saved_data["has_r"].toBool();
+    const int64_t i_res = ctx->saved_data["i_res"].toInt(), i_g = ctx->saved_data["i_g"].toInt(),
+                  i_b = ctx->saved_data["i_b"].toInt();
+    const Tensor& s = saved[0];
+    const Tensor& gamma = saved[1];
+    const bool need_dx = ctx->needs_input_grad(0) || (i_res >= 0 && ctx->needs_input_grad((size_t)i_res));
+    const bool need_dg = i_g >= 0 && ctx->needs_input_grad((size_t)i_g);
+    const bool need_db = i_b >= 0 && ctx->needs_input_grad((size_t)i_b);
+    Tensor dy = grads[0].defined() ? grads[0] : at::zeros_like(s);
+    OptTensor dres = (has_r && grads[1].defined()) ? OptTensor(grads[1]) : std::nullopt;
+    BwdOut o = norm_backward(kind, dy, s, kind == FLN_LAYERNORM ? OptTensor(saved[2]) : std::nullopt, saved[3],
+                             gamma.defined() ? OptTensor(gamma) : std::nullopt, dres, need_dx, need_dg, need_db, false,
+                             kind == FLN_LAYERNORM ? "layernorm_backward" : "rmsnorm_backward");
+    return {Tensor(), o.dx, has_r ? o.dx : Tensor(), o.dgamma, o.dbeta, Tensor()};
+  }
+};
+std::vector<Tensor> norm_autograd(int64_t kind, const Tensor& input, const OptTensor& residual, const OptTensor& gamma,
+                                  const OptTensor& beta, double epsilon) {
+  return NormAutograd::apply(kind, input, residual, gamma, beta, epsilon);
 }
 
 int64_t get_memory_usage(int batch_size, int hidden_size, bool use_mixed_precision) {
@@ -490,6 +545,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_autograd", &layernorm_autograd,
         "LayerNorm forward that records a C++ autograd node (dx, dgamma, dbeta from the fused backward)",
         py::arg("input"), py::arg("gamma") = py::none(), py::arg("beta") = py::none(), py::arg("epsilon") = 1e-5);
+  m.def("norm_autograd", &norm_autograd,
+        "(y, sum) of LayerNorm (kind 0) / RMSNorm (kind 1) with optional fused residual add, recording a C++ autograd "
+        "node; a gradient arriving for sum is added into dx inside the backward kernel",
+        py::arg("kind"), py::arg("input"), py::arg("residual") = py::none(), py::arg("gamma") = py::none(),
+        py::arg("beta") = py::none(), py::arg("epsilon") = 1e-5);
   m.def("backward", &backward_g1, "LayerNorm backward (CUDA)", py::arg("grad_output"), py::arg("input"),
         py::arg("mean"), py::arg("rstd"), py::arg("gamma") = py::none(), py::arg("beta") = py::none(),
         py::arg("output_mask") = std::array<bool, 3>{true, true, true});
