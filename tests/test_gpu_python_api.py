@@ -18,6 +18,7 @@ if torch.cuda.is_available():
     from fused_layernorm import (FusedLayerNorm, FusedLayerNormFunction, FusedRMSNorm, fused_add_layer_norm,
                                  fused_add_rms_norm, fused_add_rms_norm_fp8, fused_layer_norm, fused_rms_norm,
                                  replace_layernorm_modules)
+    from fused_layernorm import _capi as capi
     from fused_layernorm.graphs import GraphedLayerNorm, GraphedLayerNormStep
     from fused_layernorm.hostio import HostLayerNormFwdBwd
 
@@ -381,6 +382,53 @@ def test_own_graph_path():
     torch.testing.assert_close(dw, wr.grad, rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(db, br.grad, rtol=1e-4, atol=1e-4)
     st.close()
+
+
+def test_graph_replay_of_the_pipelined_step_with_fused_column_reduce():
+    """A shape served by the persistent pipeline: the backward is a cooperative launch whose
+    tail synchronises the grid on a workspace word tagged with a launch token.  A captured graph
+    replays the same token, so the word has to come back clean after every replay; three
+    replays with fresh inputs, in the library's own graph and in torch's, against eager calls."""
+    rows, cols = 8192, 4096
+    x = torch.randn(rows, cols, device="cuda", dtype=BF16)
+    dy = torch.randn_like(x)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(BF16)
+    b = (0.1 * torch.randn(cols, device="cuda")).to(BF16)
+    assert capi.describe_launch(True, rows, cols, BF16)["pipelined"] == 1
+
+    def eager():
+        y, mean, rstd = torch.empty_like(x), torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+        dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)
+        ws = torch.empty(capi.backward_workspace_bytes(rows, cols, BF16) // 4, device="cuda")
+        capi.layernorm_forward(x, w, b, y, mean, rstd, 1e-5)
+        capi.layernorm_backward(dy, x, mean, rstd, w, dx, dw, db, ws)
+        return y, dx, dw, db
+
+    st = GraphedLayerNormStep(x, dy, w, b)
+    for _ in range(3):
+        x.copy_(torch.randn_like(x))
+        dy.copy_(torch.randn_like(dy))
+        got = [t.clone() for t in st()]
+        want = eager()
+        torch.cuda.synchronize()
+        for g_, w_ in zip(got, want):
+            assert torch.equal(g_, w_)
+    st.close()
+
+    y, mean, rstd = torch.empty_like(x), torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)
+    ws = torch.empty(capi.backward_workspace_bytes(rows, cols, BF16) // 4, device="cuda")
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        capi.layernorm_forward(x, w, b, y, mean, rstd, 1e-5)
+        capi.layernorm_backward(dy, x, mean, rstd, w, dx, dw, db, ws)
+    for _ in range(3):
+        x.copy_(torch.randn_like(x))
+        g.replay()
+        want = eager()
+        torch.cuda.synchronize()
+        assert torch.equal(dx, want[1]) and torch.equal(dw, want[2]) and torch.equal(db, want[3])
+    assert capi.lib().fln_device_status() == 0
 
 
 def test_host_pipelined_path_matches_device_path():
