@@ -200,6 +200,11 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr bool FULL = MODE >= 1;
   constexpr bool ONE = MODE == 2 && KIND == FLN_LAYERNORM;
+  // MODE 4: FULL with gamma / beta parked in shared memory (in the I/O type) instead of in
+  // registers as floats, for plans that give a thread more than 32 elements (row lengths
+  // 5 * 2^a in 16-bit types: 40 elements per thread keep the 16-byte vectors and move more
+  // bytes per barrier than 20 elements in 8-byte vectors)
+  constexpr bool PSM = MODE == 4;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 + 2 x 32 floats
@@ -237,24 +242,42 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     for (int i = 0; i < pre; ++i) issue(i, i);
   }
 
-  float gam[K][VEC], bet[K][VEC];
+  float gam[PSM ? 1 : K][VEC], bet[PSM ? 1 : K][VEC];
   bool vok[K];  // does vector k of this thread exist in the row
+  unsigned char* s_gamma = stages + (size_t)S * g.stage_stride;  // PSM: [cols] gamma, then [cols] beta
+  unsigned char* s_beta = s_gamma + g.row_bytes;
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
     vok[k] = FULL ? true : iv < p.nv;
+    if constexpr (PSM) {
+      if (r_in == 0) {
+        Pack<TI, VEC> one, zero;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      gam[k][e] = 1.f;
-      bet[k][e] = 0.f;
-    }
-    if (vok[k]) {
-      if (p.gamma != nullptr)
-        unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
-      if (p.beta != nullptr)
-        unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC), bet[k]);
+        for (int e = 0; e < VEC; ++e) {
+          one.e[e] = Cvt<TI>::from_f(1.f);
+          zero.e[e] = Cvt<TI>::from_f(0.f);
+        }
+        *reinterpret_cast<Pack<TI, VEC>*>(s_gamma + (size_t)iv * VB) =
+            p.gamma != nullptr ? ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC) : one;
+        *reinterpret_cast<Pack<TI, VEC>*>(s_beta + (size_t)iv * VB) =
+            p.beta != nullptr ? ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC) : zero;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        gam[k][e] = 1.f;
+        bet[k][e] = 0.f;
+      }
+      if (vok[k]) {
+        if (p.gamma != nullptr)
+          unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
+        if (p.beta != nullptr)
+          unpack<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC), bet[k]);
+      }
     }
   }
+  if constexpr (PSM) __syncthreads();
 
   int s = 0;
   uint32_t phase = 0;
@@ -401,8 +424,17 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     for (int k = 0; k < K; ++k) {
       if (FULL || (row_ok && vok[k])) {
         float o[VEC];
+        if constexpr (PSM) {
+          float gw[VEC], bw[VEC];
+          const size_t po = (size_t)(lane_r + k * tpr) * VB;
+          unpack<TI, VEC>(stage_vec<TI, VEC>(s_gamma + po), gw);
+          unpack<TI, VEC>(stage_vec<TI, VEC>(s_beta + po), bw);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) o[e] = apply_act<ACT>(fmaf(f[k][e] * rstd, gam[k][e], bet[k][e]));
+          for (int e = 0; e < VEC; ++e) o[e] = apply_act<ACT>(fmaf(f[k][e] * rstd, gw[e], bw[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[e] = apply_act<ACT>(fmaf(f[k][e] * rstd, gam[k][e], bet[k][e]));
+        }
         Pack<TO, VEC> out;
         pack<TO, VEC>(o, out);
         st_stream<TO, VEC>(yr + (int64_t)k * tpr * VEC, out);
@@ -926,7 +958,8 @@ static int next_pow2i(int v) {
 }
 
 // tensors: how many input tensors are staged per tile (1 or 2)
-static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors, int rpt = 1) {
+static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors, int rpt = 1,
+                              bool allow_params_in_smem = true) {
   PipePlan P;
   memset(&P, 0, sizeof(P));
   const int vec = 16 / elem_bytes;
@@ -965,7 +998,10 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
   // the 16-column plans; 24 columns spill a little and are slower than 12 (6144 columns: 3986
   // vs 5237 GB/s), but faster than the two-kernel long-row path (12288 columns: 4018 vs 3365
   // GB/s), so they serve only rows that fit no other plan.  fp32 backward stays at 16.
-  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : 32, backward && elem_bytes == 2 ? 24 : 0};
+  // Forward, 16-bit types: 40 elements per thread (K = 5 vectors of 8) with gamma / beta parked
+  // in shared memory instead of registers.
+  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : (elem_bytes == 2 && allow_params_in_smem ? 40 : 32),
+                       backward && elem_bytes == 2 ? 24 : 0};
   for (int pass = 0; pass < 2; ++pass) {
     const int cap_elems = caps[pass];
     if (cap_elems == 0 || fK != 0 || rpt != 1) break;
@@ -1013,7 +1049,16 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
   P.vb = vb;
   P.K = K;
   P.threads = threads;
-  P.smem = kSmemHeader + (size_t)S * stage;
+  // forward plans beyond 32 elements per thread keep gamma and beta behind the stages
+  const bool params_in_smem = !backward && K * (vb / elem_bytes) > 32;
+  if (params_in_smem) {
+    S = (int)((budget - kSmemHeader - 2 * (size_t)row_bytes) / stage);
+    if (S > 16) S = 16;
+    // no room for two stages beside the parameters (two staged tensors of a long row): plan
+    // again with at most 32 elements per thread
+    if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, rpt, false);
+  }
+  P.smem = kSmemHeader + (size_t)S * stage + (params_in_smem ? 2 * (size_t)row_bytes : 0);
   P.g.R = R;
   P.g.tpr = tpr;
   P.g.log2_tpr = ilog2i(tpr);
@@ -1031,7 +1076,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
 
 static bool pipeline_wanted(const PipePlan& P, int64_t rows) {
   const int ov = g_path_override.load(std::memory_order_relaxed);
-  if (!P.ok || ov == 1) return false;
+  if (!P.ok || P.g.R <= 0 || P.grid <= 0 || ov == 1) return false;
   if (ov == 2 || ov == 3 || ov == 4) return true;
   // worth it once every CTA streams several tiles
   const int64_t n_tiles = (rows + P.g.R - 1) / P.g.R;
@@ -1055,7 +1100,13 @@ static int set_smem(F kernel, size_t smem) {
 template <typename TI, typename TO, int KIND, int ACT, int KK, int VB>
 static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = VB / (int)sizeof(TI);
-  if constexpr (VEC >= 4 && KK * VEC <= 32) {
+  if constexpr (VEC >= 4 && KK * VEC == 40 && sizeof(TI) == 2) {
+    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 4, VB>;
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
+    FLN_CHECK_LAUNCH();
+    return FLN_OK;
+  } else if constexpr (VEC >= 4 && KK * VEC <= 32) {
     auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 1, VB>;
     if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
     kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
@@ -1329,6 +1380,35 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
 using namespace fln;
 
 extern "C" void fln_set_path_override(int mode) { g_path_override.store(mode, std::memory_order_relaxed); }
+
+// Host-only consistency check of the pipeline planner over a grid of shapes: every plan it
+// accepts must describe a launch that exists (at least two stages, shared memory within the
+// opt-in limit, a row that divides exactly where the branch-free kernel is claimed, a grid).
+// Returns the number of violations.  Needs no GPU.
+extern "C" int fln_planner_selftest(void) {
+  static const int kCols[] = {8,    16,   64,   96,   256,  512,  768,  1000, 1024, 1280, 1536,  1600,  2048, 2560,
+                              3072, 4096, 5120, 6144, 7168, 8192, 9216, 10240, 12288, 14336, 16384, 20480, 32768};
+  static const int64_t kRows[] = {1, 7, 64, 600, 2049, 4096, 16384, 131072};
+  int bad = 0;
+  for (int cols : kCols)
+    for (int64_t rows : kRows)
+      for (int es = 2; es <= 4; es += 2)
+        for (int backward = 0; backward <= 1; ++backward)
+          for (int tensors = backward ? 2 : 1; tensors <= (backward ? 3 : 2); ++tensors) {
+            const PipePlan P = plan_pipeline(backward != 0, rows, cols, es, tensors);
+            if (!P.ok) continue;
+            const int vec = P.vb / es;
+            bool ok = P.g.S >= 2 && P.g.R >= 1 && P.grid >= 1 && P.smem <= 227u * 1024u && P.threads >= 32 &&
+                      P.threads <= 512 && P.K >= 1 && vec >= 1 && cols % vec == 0 &&
+                      (int64_t)P.K * P.g.tpr >= cols / vec && P.g.tpr * P.g.R / P.rpt == P.threads &&
+                      P.smem >= (size_t)kSmemHeader + (size_t)P.g.S * P.g.stage_stride;
+            if (P.full) ok = ok && (int64_t)P.K * P.g.tpr * vec == cols && rows % P.g.R == 0;
+            // odd K or short vectors exist only as branch-free instantiations
+            if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) && !P.full) ok = false;
+            if (!ok) ++bad;
+          }
+  return bad;
+}
 
 #ifdef FLN_CTA_TRACE
 extern "C" int fln_debug_cta_trace(unsigned long long* host_out) {

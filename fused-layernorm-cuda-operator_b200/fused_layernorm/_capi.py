@@ -30,6 +30,7 @@ SYMBOLS = [
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
+    "fln_planner_selftest",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 

@@ -279,6 +279,11 @@ void fln_set_path_override(int mode);
  * Query fln_backward_workspace_bytes again after changing it.  No counterpart in the reference. */
 void fln_set_sm_reserve(int sms);
 
+/* Diagnostic, host only (no GPU needed): checks the launch planner of the pipelined kernels
+ * over a grid of shapes and returns the number of plans that violate its invariants (0 = fine).
+ * No counterpart in the reference. */
+int fln_planner_selftest(void);
+
 /* Reads and clears the device status word of the current device (synchronizes the device).
  * 0 = no kernel reported a problem; 1 = a pipelined kernel gave up waiting for a bulk copy
  * (its outputs are then incomplete); -1 = the status could not be read.  The reference has

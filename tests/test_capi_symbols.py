@@ -67,6 +67,13 @@ def test_launch_planner_without_a_device():
     assert bwd["vec_elems"] * bwd["vecs_per_thread"] <= 32
 
 
+def test_pipeline_planner_invariants_over_a_grid_of_shapes():
+    """Every plan the pipeline planner accepts (forward with one or two staged tensors, backward
+    with two or three, 16-bit and fp32, row lengths that are and are not powers of two) describes
+    a launch that exists; checked on the host, no GPU needed."""
+    assert capi.lib().fln_planner_selftest() == 0
+
+
 def test_argument_errors_are_status_codes_not_crashes():
     lib = capi.lib()
     null = None
