@@ -623,6 +623,21 @@ def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape,
     assert capi.lib().fln_device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(1536, 1280), (600, 5120), (304, 6144), (512, 8192)])
+def test_pipelined_forward_without_parameters(path_override, shape):
+    """elementwise_affine=False through the pipelined kernels, including the plan that keeps
+    gamma / beta in shared memory (filled with ones / zeros when they are absent)."""
+    path_override(2)
+    rows, cols = shape
+    x, gamma, beta, _, res = U.make_inputs(_seed(rows, cols) + 11, rows, cols, BF16, residual=True)
+    for g_, b_ in ((None, None), (gamma, None), (None, beta)):
+        got = U.run_forward(x, g_, b_, None, "layernorm")
+        U.assert_out_close(got["y"], O.norm_forward(x, g_, b_, None, "layernorm")["y"], BF16)
+    got = U.run_forward(x, None, None, res, "rmsnorm")
+    U.assert_out_close(got["y"], O.norm_forward(x, None, None, res, "rmsnorm")["y"], BF16)
+    assert capi.lib().fln_device_status() == 0
+
+
 def test_pipeline_gelu_and_downcast(path_override):
     path_override(2)
     x, gamma, beta, _, _ = U.make_inputs(15, 900, 2048, F32)
