@@ -1168,6 +1168,18 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
   const int es = io_dtype == FLN_F32 ? 4 : 2;
   PipePlan P = plan_pipeline(false, p0.rows, p0.cols, es, p0.res != nullptr ? 2 : 1);
   if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
+  // Measured exceptions (automatic selection only).  A plain RMSNorm forward has one barrier per
+  // row and little arithmetic; the non-persistent register-resident kernel then streams faster
+  // than the ring (16384 x 8192 bf16: 88 vs 100 us; fp32 at every row length tried) unless its
+  // power-of-two plan has to pad the row (1280, 5120, 12288 columns in 16-bit types).  The same
+  // holds for the fp32 LayerNorm forward up to 4096 columns.
+  if (g_path_override.load(std::memory_order_relaxed) == 0 && p0.res == nullptr && act == FLN_ACT_NONE &&
+      io_dtype == out_dtype) {
+    const Plan rp = make_plan(false, p0.rows, p0.cols, es, true);
+    const bool exact = !rp.generic && rp.vec == 16 / es && (int64_t)rp.K * rp.tpr * rp.vec == p0.cols;
+    if (kind == FLN_RMSNORM && !rp.generic && rp.vec == 16 / es && (exact || es == 4)) return FLN_PIPE_NOT_APPLICABLE;
+    if (kind == FLN_LAYERNORM && es == 4 && exact && p0.cols <= 4096) return FLN_PIPE_NOT_APPLICABLE;
+  }
   FwdParams p = p0;
   p.nv = p.cols / (P.vb / es);
   if (io_dtype == FLN_F32 && out_dtype == FLN_F32) return fwd_pipe_typed<float, float>(kind, act, p, P, st);
@@ -1299,6 +1311,11 @@ static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
   PipePlan P = backward ? plan_bwd_pipeline(rows, cols, elem_bytes, false) : plan_pipeline(false, rows, cols, elem_bytes, 1);
   if (!pipeline_wanted(P, rows)) return false;
+  if (!backward && elem_bytes == 4 && cols <= 4096 && g_path_override.load(std::memory_order_relaxed) == 0) {
+    // the fp32 LayerNorm forward of short exact rows goes to the register kernel (launch_fwd_pipeline)
+    const Plan rp = make_plan(false, rows, cols, elem_bytes, true);
+    if (!rp.generic && rp.vec == 4 && (int64_t)rp.K * rp.tpr * rp.vec == cols) return false;
+  }
   // the odd plans exist only as branch-free instantiations; K = 8 only for fp32 forward
   if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) && !P.full) return false;
   out->vector_bytes = P.vb;
