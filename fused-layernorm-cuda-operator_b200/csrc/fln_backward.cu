@@ -396,20 +396,6 @@ __global__ void __launch_bounds__(256) colreduce_kernel(const float* __restrict_
   }
 }
 
-#ifdef FLN_CTA_TRACE
-// Debug builds only: per-CTA start / end time (ns) of the last column reduction.
-__device__ unsigned long long g_colreduce_trace[2][1024];
-__device__ __forceinline__ void colreduce_trace(int slot) {
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_colreduce_trace[slot][blockIdx.x] = t;
-  }
-}
-#else
-__device__ __forceinline__ void colreduce_trace(int) {}
-#endif
-
 // The same sum for 16-byte aligned partial rows with ncols % 4 == 0: a CTA owns 64 columns
 // (16 float4 lanes) and splits the partial rows over 16 groups, so a thread issues all of
 // its (up to 10 per pass) independent 16-byte loads before the first add.  With 148 partial
@@ -420,7 +406,6 @@ __global__ void __launch_bounds__(256) colreduce4_kernel(const float* __restrict
                                                          int ncols, int cols, float* dgb_f32,
                                                          T* dgamma, T* dbeta) {
   __shared__ __align__(16) float s[16][64];
-  colreduce_trace(0);
   const int cl = threadIdx.x & 15;
   const int rg = threadIdx.x >> 4;
   const int c4 = blockIdx.x * 16 + cl;  // float4 column
@@ -458,7 +443,6 @@ __global__ void __launch_bounds__(256) colreduce4_kernel(const float* __restrict
       if (dbeta != nullptr) dbeta[c - cols] = Cvt<T>::from_f(t);
     }
   }
-  colreduce_trace(1);
 }
 
 template <typename T>
@@ -800,8 +784,27 @@ extern "C" int fln_cast_from_f32(const float* src, void* dst, int64_t n, int dty
   return FLN_OK;
 }
 
-#ifdef FLN_CTA_TRACE
-extern "C" int fln_debug_colreduce_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, fln::g_colreduce_trace, sizeof(unsigned long long) * 2 * 1024);
+extern "C" int fln_sum_rows_f32(const float* rows_in, int64_t n_rows, int64_t ncols, float* out_f32,
+                                void* out_cast, int dtype, void* stream) {
+  if (n_rows <= 0 || ncols <= 0 || ncols > INT32_MAX || n_rows > INT32_MAX) return FLN_ERR_SHAPE;
+  if (rows_in == nullptr || (out_f32 == nullptr && out_cast == nullptr)) return FLN_ERR_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int nc = (int)ncols, P = (int)n_rows;
+  // the column-reduce kernels with every column on the "dgamma" side of the split
+  switch (dtype) {
+    case FLN_F32:
+      launch_colreduce<float>(rows_in, P, nc, nc, out_f32, reinterpret_cast<float*>(out_cast), nullptr, st);
+      break;
+    case FLN_BF16:
+      launch_colreduce<__nv_bfloat16>(rows_in, P, nc, nc, out_f32, reinterpret_cast<__nv_bfloat16*>(out_cast),
+                                      nullptr, st);
+      break;
+    case FLN_F16:
+      launch_colreduce<__half>(rows_in, P, nc, nc, out_f32, reinterpret_cast<__half*>(out_cast), nullptr, st);
+      break;
+    default:
+      return FLN_ERR_DTYPE;
+  }
+  FLN_CHECK_LAUNCH();
+  return FLN_OK;
 }
-#endif

@@ -283,135 +283,6 @@ __device__ __forceinline__ float apply_act(float v) {
 // tpr <= 32: the group is a slice of one warp.  tpr > 32: the group is tpr/32 whole warps
 // and partial results take one hop through shared memory.
 // ------------------------------------------------------------------------------------
-struct Wf {  // running (mean, M2, count)
-  float mean, m2, n;
-};
-
-__device__ __forceinline__ Wf wf_merge(Wf a, Wf b) {
-  // Chan et al. pairwise update.  Written so that equal means give delta == 0 exactly
-  // (constant rows keep M2 == 0) and empty partners (n == 0) are harmless.
-  float n = a.n + b.n;
-  float rn = n > 0.f ? __frcp_rn(n) : 0.f;
-  float delta = b.mean - a.mean;
-  Wf o;
-  o.n = n;
-  o.mean = a.mean + delta * (b.n * rn);
-  o.m2 = a.m2 + b.m2 + delta * delta * (a.n * b.n * rn);
-  return o;
-}
-
-__device__ __forceinline__ Wf wf_shfl_xor(Wf v, int off) {
-  Wf o;
-  o.mean = __shfl_xor_sync(0xffffffffu, v.mean, off);
-  o.m2 = __shfl_xor_sync(0xffffffffu, v.m2, off);
-  o.n = __shfl_xor_sync(0xffffffffu, v.n, off);
-  return o;
-}
-
-// The reductions come in two halves so that a caller can put its own CTA barrier between
-// them: *_pre (warp butterfly, lane 0 of each warp to shared memory), a barrier when
-// tpr > 32, then *_post (combine the per-warp values).
-__device__ __forceinline__ Wf wf_reduce_pre(Wf v, int tpr, float* smem) {
-  const int lane = threadIdx.x & 31;
-  const int lim = tpr < 32 ? tpr : 32;
-  for (int off = lim >> 1; off > 0; off >>= 1) v = wf_merge(v, wf_shfl_xor(v, off));
-  if (tpr > 32 && lane == 0) {
-    const int warp = threadIdx.x >> 5;
-    smem[warp] = v.mean;
-    smem[32 + warp] = v.m2;
-    smem[64 + warp] = v.n;
-  }
-  return v;
-}
-__device__ __forceinline__ Wf wf_reduce_post(Wf v, int tpr, const float* smem) {
-  const int lane = threadIdx.x & 31;
-  if (tpr > 32) {
-    const int warp = threadIdx.x >> 5;
-    const int wpr = tpr >> 5;
-    const int gbase = (warp / wpr) * wpr;
-    Wf w;
-    if (lane < wpr) {
-      w.mean = smem[gbase + lane];
-      w.m2 = smem[32 + gbase + lane];
-      w.n = smem[64 + gbase + lane];
-    } else {
-      w.mean = 0.f;
-      w.m2 = 0.f;
-      w.n = 0.f;
-    }
-    for (int off = wpr >> 1; off > 0; off >>= 1) w = wf_merge(w, wf_shfl_xor(w, off));
-    v = w;
-  }
-  const int src = tpr < 32 ? (lane & ~(tpr - 1)) : 0;
-  v.mean = __shfl_sync(0xffffffffu, v.mean, src);
-  v.m2 = __shfl_sync(0xffffffffu, v.m2, src);
-  return v;
-}
-template <int NV>
-__device__ __forceinline__ void sum_reduce_pre(float (&v)[NV], int tpr, float* smem) {
-  const int lane = threadIdx.x & 31;
-  const int lim = tpr < 32 ? tpr : 32;
-  for (int off = lim >> 1; off > 0; off >>= 1) {
-#pragma unroll
-    for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
-  }
-  if (tpr > 32 && lane == 0) {
-    const int warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) smem[i * 32 + warp] = v[i];
-  }
-}
-template <int NV>
-__device__ __forceinline__ void sum_reduce_post(float (&v)[NV], int tpr, const float* smem) {
-  if (tpr > 32) {
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int wpr = tpr >> 5;
-    const int gbase = (warp / wpr) * wpr;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) v[i] = lane < wpr ? smem[i * 32 + gbase + lane] : 0.f;
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
-    }
-  }
-}
-
-// smem: 3 * 32 floats per buffer.  Every thread of the CTA must call this.
-__device__ __forceinline__ Wf group_reduce_wf(Wf v, int tpr, float* smem) {
-  const int lane = threadIdx.x & 31;
-  const int lim = tpr < 32 ? tpr : 32;
-  for (int off = lim >> 1; off > 0; off >>= 1) v = wf_merge(v, wf_shfl_xor(v, off));
-  if (tpr > 32) {
-    const int warp = threadIdx.x >> 5;
-    const int wpr = tpr >> 5;  // warps per row
-    const int gbase = (warp / wpr) * wpr;
-    if (lane == 0) {
-      smem[warp] = v.mean;
-      smem[32 + warp] = v.m2;
-      smem[64 + warp] = v.n;
-    }
-    __syncthreads();
-    Wf w;
-    if (lane < wpr) {
-      w.mean = smem[gbase + lane];
-      w.m2 = smem[32 + gbase + lane];
-      w.n = smem[64 + gbase + lane];
-    } else {
-      w.mean = 0.f;
-      w.m2 = 0.f;
-      w.n = 0.f;
-    }
-    for (int off = wpr >> 1; off > 0; off >>= 1) w = wf_merge(w, wf_shfl_xor(w, off));
-    v = w;
-  }
-  // the two partners of a merge round differently; make the whole group agree
-  const int src = tpr < 32 ? (lane & ~(tpr - 1)) : 0;
-  v.mean = __shfl_sync(0xffffffffu, v.mean, src);
-  v.m2 = __shfl_sync(0xffffffffu, v.m2, src);
-  return v;
-}
-
 // sum of NV values per thread over the row group; all threads get bit-identical results.
 // smem: NV * 32 floats per buffer.
 template <int NV>

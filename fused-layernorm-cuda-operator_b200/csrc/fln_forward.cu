@@ -26,8 +26,8 @@ struct MaxThreads {
 // FULL: the row is exactly K * tpr vectors long, every CTA holds only valid rows and a row
 // spans at least a warp, so the body carries no bounds checks at all.
 // MODE 0: general; 1: FULL; 2: FULL and the CTA owns exactly one row (one-barrier LayerNorm
-// statistics, see below; measured slower on B200 -- register pressure -- so the launcher
-// does not select it).
+// statistics, see below; the launcher selects it for fp32 rows only: in 16-bit types the extra
+// registers make it slower).
 template <typename TI, typename TO, int VEC, int K, int KIND, int ACT, int MODE>
 __global__ void __launch_bounds__(MaxThreads<K>::value) norm_fwd_kernel(const FwdParams p) {
   constexpr bool FULL = MODE >= 1;

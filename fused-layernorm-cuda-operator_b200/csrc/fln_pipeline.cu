@@ -40,23 +40,6 @@ struct PipeGeom {
   uint32_t stage_stride;  // bytes per stage
 };
 
-#ifdef FLN_CTA_TRACE
-// Debug builds only: per-CTA start / end time (ns) and SM id of the last pipelined launch.
-__device__ unsigned long long g_cta_trace[5][1024];
-__device__ __forceinline__ void cta_trace(int slot) {
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
-    unsigned long long t;
-    unsigned int sm;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-    g_cta_trace[slot][blockIdx.x] = t;
-    g_cta_trace[2][blockIdx.x] = sm;
-  }
-}
-#else
-__device__ __forceinline__ void cta_trace(int) {}
-#endif
-
 constexpr int kSmemHeader = 2048;  // mbarriers + reduction scratch in front of the stages
 constexpr uint32_t kWaitLimit = 1u << 24;
 
@@ -193,8 +176,8 @@ __device__ __forceinline__ void grid_depart(unsigned long long* w, unsigned int 
 // reduced by a warp butterfly plus one shared-memory hop.
 // ----------------------------------------------------------------------------------------
 // MODE 0: general (bounds-checked); 1: FULL (no predication in the loop); 2: FULL and the
-// CTA owns exactly one row, which allows the one-barrier LayerNorm statistics below (measured
-// no faster on B200, so the launcher does not select it).
+// CTA owns exactly one row, which allows the one-barrier LayerNorm statistics below (no launch
+// path of this file instantiates it: it measured no faster than MODE 1 in the ring).
 template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16>
 __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
@@ -219,7 +202,6 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   const bool has_res = p.res != nullptr;
   const float inv_n = 1.0f / (float)p.cols;
   const float eps = p.eps;
-  cta_trace(0);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
@@ -445,7 +427,6 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       phase ^= 1u;
     }
   }
-  cta_trace(1);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -477,7 +458,6 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb) 
     if (tid == 0) atomicExch(&g_device_status, 2);
     return;
   }
-  cta_trace(3);
   const int ncols = NR * p.cols;
   const int n4 = ncols >> 2;
   const int P = p.P;
@@ -520,7 +500,6 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb) 
     __syncthreads();
   }
   if (tid == 0) grid_depart(p.sync, gridDim.x);
-  cta_trace(4);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -548,7 +527,6 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   const int S = g.S;
   const int my_tiles = my_tile_count((p.rows + g.R - 1) / g.R);
   const float inv_n = 1.0f / (float)p.cols;
-  cta_trace(0);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
@@ -733,7 +711,6 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
       }
     }
   }
-  cta_trace(1);
 
   if (FUSE) {
     ReduceArgs a;
@@ -750,194 +727,15 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 }
 
 // ----------------------------------------------------------------------------------------
-// backward, two rows per thread per barrier (FULL shapes with an even number of row groups).
-//
-// The one-row kernel above spends much of its time in the per-row dependency chain
-// (shared-memory read -> sums -> warp butterfly -> CTA barrier -> dx) with only 16 warps per
-// SM to hide it.  Here a tile holds two rows per row group; each thread works on the same 16
-// columns of both rows, the four running sums share one butterfly and ONE barrier, and the two
-// rows' instruction streams interleave.  Same arithmetic per element, half the barriers.
-// ----------------------------------------------------------------------------------------
-template <typename T, int K, int KIND>
-__global__ void __launch_bounds__(512) norm_bwd_pipe2_kernel(const BwdParams p, const PipeGeom g) {
-  constexpr int VEC = 16 / sizeof(T);
-  constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
-  extern __shared__ __align__(128) unsigned char smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 128 floats
-  unsigned char* stages = smem + kSmemHeader;
-
-  const int tid = threadIdx.x;
-  const int tpr = g.tpr;
-  const int lane_r = tid & (tpr - 1);
-  const int r_in = tid >> g.log2_tpr;
-  const int Rg = g.R >> 1;  // row groups per CTA; the tile's rows are r_in and Rg + r_in
-  const int S = g.S;
-  const int my_tiles = my_tile_count(p.rows / g.R);  // the launcher guarantees rows % R == 0
-  const float inv_n = 1.0f / (float)p.cols;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
-    mbar_init_fence();
-  }
-  __syncthreads();
-
-  const uint32_t tile_bytes = (uint32_t)g.R * g.row_bytes;
-  auto issue = [&](int i, int s) {
-    const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)i * gridDim.x) * g.R;
-    unsigned char* dst = stages + (size_t)s * g.stage_stride;
-    mbar_expect_tx(&full[s], 2 * tile_bytes);
-    bulk_g2s(dst, reinterpret_cast<const T*>(p.dy) + row0 * p.cols, tile_bytes, &full[s]);
-    bulk_g2s(dst + g.second_off, reinterpret_cast<const T*>(p.x) + row0 * p.cols, tile_bytes, &full[s]);
-  };
-  if (tid == 0) {
-    const int pre = my_tiles < S ? my_tiles : S;
-    for (int i = 0; i < pre; ++i) issue(i, i);
-  }
-
-  float acc_g[K][VEC], acc_b[K][VEC], gam[K][VEC];
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const int iv = lane_r + k * tpr;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      acc_g[k][e] = 0.f;
-      acc_b[k][e] = 0.f;
-      gam[k][e] = 1.f;
-    }
-    if (p.gamma != nullptr)
-      unpack<T, VEC>(ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
-  }
-
-  int64_t row = (int64_t)blockIdx.x * g.R + r_in;
-  const int64_t row_step = (int64_t)gridDim.x * g.R;
-  float mean_n[2] = {0.f, 0.f}, rstd_n[2] = {0.f, 0.f};
-  if (my_tiles > 0) {
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      if (KIND == FLN_LAYERNORM) mean_n[rr] = __ldg(p.mean + row + rr * Rg);
-      rstd_n[rr] = __ldg(p.rstd + row + rr * Rg);
-    }
-  }
-
-  int s = 0;
-  uint32_t phase = 0;
-  const uint32_t my_off = (uint32_t)r_in * g.row_bytes + (uint32_t)lane_r * 16u;
-  const uint32_t k_off = (uint32_t)tpr * 16u;
-  const uint32_t rr_off = (uint32_t)Rg * g.row_bytes;
-  for (int i = 0; i < my_tiles; ++i, row += row_step) {
-    float mean[2], rstd[2];
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      mean[rr] = mean_n[rr];
-      rstd[rr] = rstd_n[rr];
-    }
-    if (i + 1 < my_tiles) {
-#pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        if (KIND == FLN_LAYERNORM) mean_n[rr] = __ldg(p.mean + row + row_step + rr * Rg);
-        rstd_n[rr] = __ldg(p.rstd + row + row_step + rr * Rg);
-      }
-    }
-    const bool landed = mbar_wait_bounded(&full[s], phase);
-    const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
-
-    float xh[2][K][VEC], dyf[2][K][VEC];
-    float red[2 * NR];
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      float r0a = 0.f, r0b = 0.f, r1a = 0.f, r1b = 0.f;
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        unpack<T, VEC>(stage_vec<T>(st + rr * rr_off + k * k_off), dyf[rr][k]);
-        unpack<T, VEC>(stage_vec<T>(st + g.second_off + rr * rr_off + k * k_off), xh[rr][k]);
-#pragma unroll
-        for (int e = 0; e < VEC; e += 2) {
-          xh[rr][k][e] = (xh[rr][k][e] - mean[rr]) * rstd[rr];
-          xh[rr][k][e + 1] = (xh[rr][k][e + 1] - mean[rr]) * rstd[rr];
-          const float g0 = dyf[rr][k][e] * gam[k][e], g1 = dyf[rr][k][e + 1] * gam[k][e + 1];
-          r0a = fmaf(g0, xh[rr][k][e], r0a);
-          r0b = fmaf(g1, xh[rr][k][e + 1], r0b);
-          if (KIND == FLN_LAYERNORM) {
-            r1a += g0;
-            r1b += g1;
-          }
-        }
-      }
-      red[rr * NR] = r0a + r0b;
-      if (KIND == FLN_LAYERNORM) red[rr * NR + NR - 1] = r1a + r1b;
-    }
-    float* sr = s_red + (i & 1) * 128;
-    rowsum_warp<2 * NR>(red, tpr, sr);
-    if (!__syncthreads_and(landed ? 1 : 0)) {
-      pipeline_abort(full, S, s, phase, my_tiles - i < S ? my_tiles - i : S);
-      return;
-    }
-    if (tid == 0 && i + S < my_tiles) issue(i + S, s);
-    rowsum_cta<2 * NR>(red, tpr, sr);
-
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const float nc1 = -(red[rr * NR] * inv_n);
-      const float c2 = KIND == FLN_LAYERNORM ? red[rr * NR + NR - 1] * inv_n : 0.f;
-      if (p.dx != nullptr) {
-        T* __restrict__ dxr =
-            reinterpret_cast<T*>(p.dx) + (row + rr * Rg) * (int64_t)p.cols + (int64_t)lane_r * VEC;
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-          float o[VEC];
-#pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            o[e] = rstd[rr] * fmaf(xh[rr][k][e], nc1, dyf[rr][k][e] * gam[k][e] - c2);
-          Pack<T, VEC> out;
-          pack<T, VEC>(o, out);
-          st_stream<T, VEC>(dxr + (int64_t)k * tpr * VEC, out);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          acc_g[k][e] = fmaf(dyf[rr][k][e], xh[rr][k][e], acc_g[k][e]);
-          if (KIND == FLN_LAYERNORM) acc_b[k][e] += dyf[rr][k][e];
-        }
-      }
-    }
-    if (++s == S) {
-      s = 0;
-      phase ^= 1u;
-    }
-  }
-
-  if (p.partials != nullptr) {
-    const int64_t prow = (int64_t)blockIdx.x * Rg + r_in;
-    float* __restrict__ pg = p.partials + prow * (int64_t)(NR * p.cols);
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int iv = lane_r + k * tpr;
-#pragma unroll
-      for (int e = 0; e < VEC; e += 4) {
-        *reinterpret_cast<float4*>(pg + (int64_t)iv * VEC + e) =
-            make_float4(acc_g[k][e], acc_g[k][e + 1], acc_g[k][e + 2], acc_g[k][e + 3]);
-        if (KIND == FLN_LAYERNORM)
-          *reinterpret_cast<float4*>(pg + p.cols + (int64_t)iv * VEC + e) =
-              make_float4(acc_b[k][e], acc_b[k][e + 1], acc_b[k][e + 2], acc_b[k][e + 3]);
-      }
-    }
-  }
-}
-
-// ----------------------------------------------------------------------------------------
 // host: geometry and dispatch
 // ----------------------------------------------------------------------------------------
 // 0 auto, 1 register kernels only, 2 pipeline whenever it fits, 3 as 2 with the column reduce
-// as a second kernel, 4 as 2 with the two-rows-per-barrier backward
+// as a second kernel
 static std::atomic<int> g_path_override{0};
 
 struct PipePlan {
   bool ok;
   bool full;  // branch-free instantiation applies
-  int rpt;    // rows per thread per barrier (backward: 1 or 2)
   int vb;     // bytes per vector: 16, or 8 / 4 where that makes the row divide evenly
   int K;
   int threads;
@@ -958,7 +756,7 @@ static int next_pow2i(int v) {
 }
 
 // tensors: how many input tensors are staged per tile (1 or 2)
-static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors, int rpt = 1,
+static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors,
                               bool allow_params_in_smem = true) {
   PipePlan P;
   memset(&P, 0, sizeof(P));
@@ -1004,7 +802,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
                        backward && elem_bytes == 2 ? 24 : 0};
   for (int pass = 0; pass < 2; ++pass) {
     const int cap_elems = caps[pass];
-    if (cap_elems == 0 || fK != 0 || rpt != 1) break;
+    if (cap_elems == 0 || fK != 0) break;
     if (pass == 0 ? !(K == 0 || (int64_t)K * tpr != nv) : K != 0) break;
     const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
     int best_elems = 0;
@@ -1029,7 +827,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
   }
   if (K == 0) return P;
   const int threads = tpr > cta_threads ? tpr : cta_threads;
-  const int R = (threads / tpr) * rpt;
+  const int R = threads / tpr;
   const uint32_t row_bytes = (uint32_t)cols * elem_bytes;
   const uint32_t tile_bytes = row_bytes * R;
   const uint32_t stage = tile_bytes * tensors;
@@ -1044,7 +842,6 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
     if (S < 2) return P;
   }
   P.ok = true;
-  P.rpt = rpt;
   P.full = tpr >= 32 && (int64_t)K * tpr == cols / (vb / elem_bytes) && rows % R == 0;
   P.vb = vb;
   P.K = K;
@@ -1056,7 +853,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
     if (S > 16) S = 16;
     // no room for two stages beside the parameters (two staged tensors of a long row): plan
     // again with at most 32 elements per thread
-    if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, rpt, false);
+    if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, false);
   }
   P.smem = kSmemHeader + (size_t)S * stage + (params_in_smem ? 2 * (size_t)row_bytes : 0);
   P.g.R = R;
@@ -1077,7 +874,7 @@ static PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_by
 static bool pipeline_wanted(const PipePlan& P, int64_t rows) {
   const int ov = g_path_override.load(std::memory_order_relaxed);
   if (!P.ok || P.g.R <= 0 || P.grid <= 0 || ov == 1) return false;
-  if (ov == 2 || ov == 3 || ov == 4) return true;
+  if (ov == 2 || ov == 3) return true;
   // worth it once every CTA streams several tiles
   const int64_t n_tiles = (rows + P.g.R - 1) / P.g.R;
   return n_tiles >= 4LL * P.grid || n_tiles >= 8LL * sm_count();
@@ -1268,17 +1065,10 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
       kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                       \
     }                                                                                        \
   }
-#define FLN_LAUNCH2(KK)                                                                      \
-  {                                                                                          \
-    auto kern = norm_bwd_pipe2_kernel<T, (VEC * KK <= 16 ? KK : 1), KIND>;                   \
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                             \
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                         \
-  }
 #define FLN_CASE(KK)                                       \
   case KK:                                                 \
     if (VEC * KK > 16) return FLN_PIPE_NOT_APPLICABLE;     \
-    if (P.full && P.rpt == 2) FLN_LAUNCH2(KK)              \
-    else if (p.dres_in != nullptr) {                       \
+    if (p.dres_in != nullptr) {                            \
       if (P.full) FLN_LAUNCH(KK, true, true)               \
       else FLN_LAUNCH(KK, false, true)                     \
     } else if (P.full) FLN_LAUNCH(KK, true, false)         \
@@ -1291,21 +1081,12 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   }
 #undef FLN_CASE
 #undef FLN_LAUNCH
-#undef FLN_LAUNCH2
   FLN_CHECK_LAUNCH();
   return FLN_OK;
 }
 
-// Backward plan.  The two-rows-per-barrier kernel measured slower on B200 (257 vs 179 us at
-// 16384 x 8192 bf16: it spills at 128 registers and leaves room for only 3 stages), so it is
-// selected only by path override 4, for A/B timing.
 static PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
-  if (with_dres) return plan_pipeline(true, rows, cols, es, 3, 1);
-  if (g_path_override.load(std::memory_order_relaxed) == 4) {
-    PipePlan P2 = plan_pipeline(true, rows, cols, es, 2, 2);
-    if (P2.ok && P2.full) return P2;
-  }
-  return plan_pipeline(true, rows, cols, es, 2, 1);
+  return plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
 }
 
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
@@ -1333,7 +1114,7 @@ int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, b
   const int es = dtype == FLN_F32 ? 4 : 2;
   PipePlan P = plan_bwd_pipeline(rows, cols, es, with_dres);
   if (!pipeline_wanted(P, rows)) return 0;
-  return (int64_t)P.grid * (P.g.R / P.rpt);
+  return (int64_t)P.grid * P.g.R;
 }
 
 static bool cooperative_launch_supported() {
@@ -1369,7 +1150,7 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
   p.nv = p.cols / (P.vb / es);
   // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the
   // one-row kernel, stage memory large enough for the 16 x 128 floats of the combine step.
-  const bool fuse = p.sync != nullptr && p.partials != nullptr && P.rpt == 1 && P.grid <= usable_sms() &&
+  const bool fuse = p.sync != nullptr && p.partials != nullptr && P.grid <= usable_sms() &&
                     P.grid < 4096 && P.smem >= (size_t)kSmemHeader + 16 * 128 * sizeof(float) &&
                     g_path_override.load(std::memory_order_relaxed) != 3 && cooperative_launch_supported();
   if (fuse) {
@@ -1417,7 +1198,7 @@ extern "C" int fln_planner_selftest(void) {
             const int vec = P.vb / es;
             bool ok = P.g.S >= 2 && P.g.R >= 1 && P.grid >= 1 && P.smem <= 227u * 1024u && P.threads >= 32 &&
                       P.threads <= 512 && P.K >= 1 && vec >= 1 && cols % vec == 0 &&
-                      (int64_t)P.K * P.g.tpr >= cols / vec && P.g.tpr * P.g.R / P.rpt == P.threads &&
+                      (int64_t)P.K * P.g.tpr >= cols / vec && P.g.tpr * P.g.R == P.threads &&
                       P.smem >= (size_t)kSmemHeader + (size_t)P.g.S * P.g.stage_stride;
             if (P.full) ok = ok && (int64_t)P.K * P.g.tpr * vec == cols && rows % P.g.R == 0;
             // odd K or short vectors exist only as branch-free instantiations
@@ -1426,12 +1207,6 @@ extern "C" int fln_planner_selftest(void) {
           }
   return bad;
 }
-
-#ifdef FLN_CTA_TRACE
-extern "C" int fln_debug_cta_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, fln::g_cta_trace, sizeof(unsigned long long) * 5 * 1024);
-}
-#endif
 
 extern "C" int fln_device_status(void) {
   int v = 0;

@@ -30,7 +30,7 @@ SYMBOLS = [
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
-    "fln_planner_selftest",
+    "fln_planner_selftest", "fln_sum_rows_f32",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -72,6 +72,7 @@ def lib() -> C.CDLL:
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_norm_backward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_cast_from_f32.argtypes = [vp, vp, i64, i32, vp]
+    L.fln_sum_rows_f32.argtypes = [vp, i64, i64, vp, vp, i32, vp]
     L.fln_graph_begin.argtypes = [C.POINTER(vp)]
     L.fln_graph_stream.restype = vp
     L.fln_graph_stream.argtypes = [vp]
@@ -211,6 +212,14 @@ def layernorm_backward_static(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, strea
 def cast_from_f32(src, dst, stream=None):
     check(lib().fln_cast_from_f32(ptr(src), ptr(dst), src.numel(), DTYPES[dst.dtype], stream_handle(stream)),
           "fln_cast_from_f32")
+
+
+def sum_rows_f32(rows_in, out_f32=None, out_cast=None, stream=None):
+    """Fixed-order column sum of an fp32 matrix [n, ncols] into out_f32 and / or out_cast."""
+    n, ncols = rows_in.shape
+    dt = DTYPES[out_cast.dtype] if out_cast is not None else F32
+    check(lib().fln_sum_rows_f32(ptr(rows_in), n, ncols, ptr(out_f32), ptr(out_cast), dt, stream_handle(stream)),
+          "fln_sum_rows_f32")
 
 
 def describe_launch(backward, rows, cols, dtype, aligned16=True) -> dict:

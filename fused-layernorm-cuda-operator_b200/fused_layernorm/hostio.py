@@ -32,14 +32,17 @@ class HostLayerNormFwdBwd:
         self.slots = torch.zeros(n, 2 * cols, dtype=torch.float32, device=d)
         self.dgb = torch.empty(2 * cols, dtype=torch.float32, device=d)
         self.dparams = torch.empty(2 * cols, dtype=dtype, device=d)
-        ws = capi.backward_workspace_bytes(self.chunk_rows, cols, dtype)
+        # the last chunk may be shorter and planned differently: size for the largest request
+        ws = max(capi.backward_workspace_bytes(b - a, cols, dtype) for a, b in self.bounds)
         self.ws = torch.empty(max(ws // 4, 1), dtype=torch.float32, device=d)
         self.s_in = torch.cuda.Stream(d)
         self.s_cmp = torch.cuda.Stream(d)
         self.s_out = torch.cuda.Stream(d)
         self.ev_in = [torch.cuda.Event() for _ in range(n)]
         self.ev_cmp = [torch.cuda.Event() for _ in range(n)]
-        self.launches_per_call = 3 * n + 1  # forward + 2 backward launches per chunk, one cast
+        # forward + backward per chunk (the backward reduces its partial sums in its own tail at
+        # these sizes; where it cannot, it adds a launch), one sum of the chunks' slots with the cast
+        self.launches_per_call = 2 * n + 1
 
     @property
     def h2d_bytes(self) -> int:
@@ -75,8 +78,7 @@ class HostLayerNormFwdBwd:
                 y_host[a:b].copy_(self.y[a:b], non_blocking=True)
                 dx_host[a:b].copy_(self.dx[a:b], non_blocking=True)
         with torch.cuda.stream(self.s_cmp):
-            torch.sum(self.slots, dim=0, out=self.dgb)
-            capi.cast_from_f32(self.dgb, self.dparams, stream=self.s_cmp)
+            capi.sum_rows_f32(self.slots, self.dgb, self.dparams, stream=self.s_cmp)
         self.s_out.wait_stream(self.s_cmp)
         with torch.cuda.stream(self.s_out):
             dparams_host.copy_(self.dparams, non_blocking=True)

@@ -39,7 +39,7 @@ typedef enum { FLN_ACT_NONE = 0, FLN_ACT_GELU_TANH = 1, FLN_ACT_GELU_ERF = 2 } f
 typedef enum {
   FLN_OK = 0,
   FLN_ERR_DTYPE = 1,       /* dtype not supported by this entry point            */
-  FLN_ERR_SHAPE = 2,       /* rows < 0, cols <= 0, or cols beyond the int range  */
+  FLN_ERR_SHAPE = 2,       /* rows < 0 or > INT32_MAX, cols <= 0 or > INT32_MAX  */
   FLN_ERR_NULL = 3,        /* a required pointer is NULL                         */
   FLN_ERR_WORKSPACE = 4,   /* scratch buffer missing or too small                */
   FLN_ERR_LAUNCH = 5,      /* the CUDA runtime reported an error at launch       */
@@ -209,6 +209,15 @@ int fln_layernorm_backward_static(const void* dy, const void* x, const float* me
  * parameter-typed gradients.  No counterpart in the reference. */
 int fln_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, void* stream);
 
+/* out[c] = sum over r of rows_in[r][c] for an fp32 matrix [n_rows, ncols] (row pitch ncols),
+ * added in a fixed order (reproducible); written as fp32 (out_f32), rounded to `dtype`
+ * (out_cast), or both.  It is stage 2 of the backward -- the fixed-order sum the reference's
+ * backward declaration calls for (csrc/layernorm.h:24-32) -- opened to callers that hold several
+ * [dgamma | dbeta] buffers of their own: one per micro-batch, or one per row chunk of a batch
+ * that is streamed through the device. */
+int fln_sum_rows_f32(const float* rows_in, int64_t n_rows, int64_t ncols, float* out_f32,
+                     void* out_cast, int dtype, void* stream);
+
 /* ----------------------------------------------------------------------------------
  * CUDA-graph launch path for latency-bound shapes
  * -------------------------------------------------------------------------------- */
@@ -268,8 +277,7 @@ void fln_set_plan_override(int vecs_per_thread, int threads_per_row);
  * bulk-async pipeline once every CTA streams several tiles, register-resident kernels
  * otherwise), 1 = register-resident kernels only, 2 = the pipeline whenever the row fits,
  * 3 = like 2 but dgamma / dbeta are reduced by a second kernel instead of in the tail of the
- * backward launch, 4 = like 2 but the backward uses the two-rows-per-barrier variant where
- * the shape allows.  Query fln_backward_workspace_bytes again after changing it. */
+ * backward launch.  Query fln_backward_workspace_bytes again after changing it. */
 void fln_set_path_override(int mode);
 
 /* Persistent kernels size their grids to fill every SM exactly and split the rows statically,

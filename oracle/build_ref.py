@@ -11,6 +11,7 @@ setup.py (its own build system), only nvcc and g++ directly.
 from __future__ import annotations
 
 import argparse
+import os
 import subprocess
 import sys
 import sysconfig
@@ -23,7 +24,8 @@ NAME = "ref_g2_layernorm_cuda"
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FLN_REFERENCE_DIR"), required="FLN_REFERENCE_DIR" not in os.environ,
+                    help="checkout of the reference (or set FLN_REFERENCE_DIR)")
     a = ap.parse_args()
     ref = Path(a.reference)
     srcs = [ref / "csrc" / "bindings.cpp", ref / "csrc" / "layernorm_cuda_kernel.cu"]
