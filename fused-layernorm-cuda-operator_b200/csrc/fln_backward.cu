@@ -737,6 +737,9 @@ extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const 
   p.dgb_f32 = nullptr;
   p.dgamma = nullptr;
   p.dbeta = nullptr;
+  p.wait_ns = 0;
+  p.status = nullptr;
+  p.fault = nullptr;
   const bool aligned = is_aligned16(dy) && is_aligned16(x) && is_aligned16(gamma) &&
                        is_aligned16(dres_in) && is_aligned16(dx);
 #define FLN_RUN(T)                                                                         \

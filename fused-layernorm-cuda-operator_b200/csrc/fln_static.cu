@@ -14,6 +14,7 @@
 // In host code the name of a __device__ array is only a host-side handle, not an address the
 // GPU can use, so the device address is looked up with cudaGetSymbolAddress -- once per
 // device, with that device current, on the first call made for it.
+#include <atomic>
 #include <mutex>
 
 #include "fln_common.cuh"
@@ -21,6 +22,9 @@
 namespace {
 
 static __device__ __align__(256) unsigned char g_static_scratch[FLN_STATIC_SCRATCH_BYTES];
+
+// what the entry point accepts; tests lower it to see the refusal (fln_set_static_scratch_limit)
+std::atomic<size_t> g_scratch_limit{FLN_STATIC_SCRATCH_BYTES};
 
 constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
@@ -55,7 +59,7 @@ extern "C" int fln_layernorm_backward_static(const void* dy, const void* x, cons
   if (dtype != FLN_F32 && dtype != FLN_BF16 && dtype != FLN_F16) return FLN_ERR_DTYPE;
   // the same sizing rule as the regular entry point, checked against the fixed capacity
   const size_t need = fln_backward_workspace_bytes(rows, cols, dtype);
-  if (need > (size_t)FLN_STATIC_SCRATCH_BYTES) return FLN_ERR_STATIC_SCRATCH;
+  if (need > g_scratch_limit.load(std::memory_order_relaxed)) return FLN_ERR_STATIC_SCRATCH;
   void* scratch = scratch_for_current_device();
   if (scratch == nullptr) return FLN_ERR_LAUNCH;
   // Nothing in the scratch has to start at zero: stage 1 overwrites every partial row that
@@ -63,4 +67,10 @@ extern "C" int fln_layernorm_backward_static(const void* dy, const void* x, cons
   return fln_norm_backward(FLN_LAYERNORM, dy, x, mean, rstd, gamma, nullptr, dx, dgamma, dbeta,
                            nullptr, scratch, (size_t)FLN_STATIC_SCRATCH_BYTES, rows, cols, dtype,
                            stream);
+}
+
+extern "C" void fln_set_static_scratch_limit(size_t bytes) {
+  // never beyond the array itself; 0 restores the full capacity
+  if (bytes == 0 || bytes > (size_t)FLN_STATIC_SCRATCH_BYTES) bytes = FLN_STATIC_SCRATCH_BYTES;
+  g_scratch_limit.store(bytes, std::memory_order_relaxed);
 }

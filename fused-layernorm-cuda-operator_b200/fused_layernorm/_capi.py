@@ -30,7 +30,8 @@ SYMBOLS = [
     "fln_get_memory_usage", "fln_get_performance_hints", "fln_describe_launch", "fln_set_plan_override",
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
-    "fln_planner_selftest", "fln_sum_rows_f32",
+    "fln_planner_selftest", "fln_sum_rows_f32", "fln_set_stage_override", "fln_set_wait_limit_ns",
+    "fln_set_test_fault", "fln_set_static_scratch_limit",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -73,6 +74,12 @@ def lib() -> C.CDLL:
     L.fln_norm_backward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_cast_from_f32.argtypes = [vp, vp, i64, i32, vp]
     L.fln_sum_rows_f32.argtypes = [vp, i64, i64, vp, vp, i32, vp]
+    L.fln_set_stage_override.restype = None
+    L.fln_set_stage_override.argtypes = [i32]
+    L.fln_set_wait_limit_ns.argtypes = [C.c_ulonglong]
+    L.fln_set_test_fault.argtypes = [i32]
+    L.fln_set_static_scratch_limit.restype = None
+    L.fln_set_static_scratch_limit.argtypes = [sz]
     L.fln_graph_begin.argtypes = [C.POINTER(vp)]
     L.fln_graph_stream.restype = vp
     L.fln_graph_stream.argtypes = [vp]

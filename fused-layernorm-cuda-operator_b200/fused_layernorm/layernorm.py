@@ -107,7 +107,7 @@ class FusedLayerNorm(nn.Module):
     """
 
     def __init__(self, normalized_shape, eps: float = 1e-5, elementwise_affine: bool = True,
-                 device=None, dtype=None) -> None:
+                 bias: bool = True, device=None, dtype=None) -> None:
         factory_kwargs = {"device": device, "dtype": dtype}
         super().__init__()
         if isinstance(normalized_shape, int):
@@ -117,7 +117,10 @@ class FusedLayerNorm(nn.Module):
         self.elementwise_affine = elementwise_affine
         if self.elementwise_affine:
             self.weight = Parameter(torch.empty(self.normalized_shape, **factory_kwargs))
-            self.bias = Parameter(torch.empty(self.normalized_shape, **factory_kwargs))
+            if bias:  # torch.nn.LayerNorm(..., bias=False): weight only
+                self.bias = Parameter(torch.empty(self.normalized_shape, **factory_kwargs))
+            else:
+                self.register_parameter("bias", None)
         else:
             self.register_parameter("weight", None)
             self.register_parameter("bias", None)
@@ -126,13 +129,14 @@ class FusedLayerNorm(nn.Module):
     def reset_parameters(self) -> None:
         if self.elementwise_affine:
             nn.init.ones_(self.weight)
-            nn.init.zeros_(self.bias)
+            if self.bias is not None:
+                nn.init.zeros_(self.bias)
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         if (input.dim() == 2 and len(self.normalized_shape) == 1 and input.is_cuda and not torch.compiler.is_compiling()
                 and input.size(1) == self.normalized_shape[0] and input.is_contiguous()
-                and not (torch.is_grad_enabled() and (input.requires_grad or (self.weight is not None and (
-                    self.weight.requires_grad or self.bias.requires_grad))))):
+                and not (torch.is_grad_enabled() and (input.requires_grad or any(
+                    q is not None and q.requires_grad for q in (self.weight, self.bias))))):
             # inference: nothing to record, one call into the extension
             return fused_layernorm_cuda.layernorm(input, self.weight, self.bias, self.eps)
         if (input.dim() == 2 and len(self.normalized_shape) == 1 and input.is_cuda and not torch.compiler.is_compiling()
@@ -198,6 +202,7 @@ def replace_layernorm_modules(model: nn.Module) -> int:
         if isinstance(child, _ORIGINAL_TORCH_LAYERNORM) and not isinstance(child, FusedLayerNorm):
             w = child.weight
             new = FusedLayerNorm(child.normalized_shape, child.eps, child.elementwise_affine,
+                                 bias=child.bias is not None,
                                  device=w.device if w is not None else None,
                                  dtype=w.dtype if w is not None else None)
             if child.elementwise_affine:

@@ -121,3 +121,109 @@ class ShardedLayerNorm:
             return dx, finish
         dgamma, dbeta = finish()
         return dx, dgamma, dbeta
+
+
+class ShardedLayerNormStep:
+    """The training step of one rank, preallocated: LayerNorm forward + backward over this rank's
+    shard with the all-reduce of the parameter gradients off the critical path.
+
+        step = ShardedLayerNormStep(rows, hidden, torch.bfloat16)   # after init_process_group
+        for batch in loader:
+            y = step.forward(x, gamma, beta)           # current stream, no communication
+            dx = step.backward(dy, gamma)              # current stream; the reduction is queued
+            ...
+        dgamma, dbeta = step.finish()                  # joins the reductions still in flight
+
+    The fp32 [dgamma | dbeta] sums of a step are all-reduced and rounded to the parameter dtype
+    on a side stream, behind an event that follows the backward; the stream the caller launches
+    on never waits for them (a training loop needs the parameter gradients at its optimizer
+    step, not before), so the collective overlaps the next forward.  Two fp32 buffers alternate;
+    before a buffer is written again the caller's stream waits for the event that marks its
+    previous reduction as finished, which by then lies a whole step in the past.  Everything is
+    launched through the C ABI on buffers allocated here once, so a step allocates nothing.
+
+    With one rank (or no process group) there is nothing to reduce: the backward writes dgamma
+    and dbeta itself.  No kernel of this class waits on a peer; the only cross-rank
+    synchronization is the collective.
+    """
+
+    def __init__(self, rows: int, hidden: int, dtype=torch.bfloat16, eps: float = 1e-5, group=None,
+                 sm_reserve: Optional[int] = 2, device=None):
+        from . import _capi as capi  # raises when the library has not been built: no fallback
+        self._capi = capi
+        self.rows, self.hidden, self.dtype, self.eps, self.group = int(rows), int(hidden), dtype, float(eps), group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        d = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.device = d
+        if self.world > 1 and sm_reserve is not None:
+            capi.lib().fln_set_sm_reserve(int(sm_reserve))  # see ShardedLayerNorm.__init__
+        self.y = torch.empty(rows, hidden, dtype=dtype, device=d)
+        self.dx = torch.empty(rows, hidden, dtype=dtype, device=d)
+        self.mean = torch.empty(rows, dtype=torch.float32, device=d)
+        self.rstd = torch.empty(rows, dtype=torch.float32, device=d)
+        self.dgb = [torch.zeros(2 * hidden, dtype=torch.float32, device=d) for _ in range(2)]
+        self.dparams = torch.zeros(2 * hidden, dtype=dtype, device=d)
+        ws = capi.backward_workspace_bytes(rows, hidden, dtype)
+        self.ws = torch.empty(max(ws // 4, 1), dtype=torch.float32, device=d)
+        self.side = torch.cuda.Stream(d) if self.world > 1 else None
+        self.ev_bwd = [torch.cuda.Event() for _ in range(2)]
+        self.ev_red = [torch.cuda.Event() for _ in range(2)]
+        self.steps = 0
+        self._x = None
+        # kernels of this library per step: forward, backward (the column sums are reduced in
+        # its own tail), and with more than one rank the rounding of the all-reduced sums
+        self.launches_per_step = 2 + (1 if self.world > 1 else 0)
+
+    def forward(self, x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor]) -> torch.Tensor:
+        if x.shape != (self.rows, self.hidden) or x.dtype != self.dtype:
+            raise ValueError(f"x must be [{self.rows}, {self.hidden}] {self.dtype}, got {tuple(x.shape)} {x.dtype}")
+        if self.rows:
+            self._capi.layernorm_forward(x, gamma, beta, self.y, self.mean, self.rstd, self.eps)
+        self._x = x
+        return self.y
+
+    def backward(self, dy: torch.Tensor, gamma: Optional[torch.Tensor]) -> torch.Tensor:
+        capi = self._capi
+        if self._x is None:
+            raise RuntimeError("backward() before forward()")
+        if dy.shape != self._x.shape or dy.dtype != self.dtype:
+            raise ValueError(f"dy must match x: {tuple(self._x.shape)} {self.dtype}")
+        h = self.hidden
+        if self.world == 1:
+            if self.rows:
+                capi.norm_backward(capi.LAYERNORM, dy, self._x, self.mean, self.rstd, gamma, None, self.dx,
+                                   self.dparams[:h], self.dparams[h:], self.dgb[0], self.ws)
+            self.steps += 1
+            return self.dx
+        k = self.steps & 1
+        buf = self.dgb[k]
+        main = torch.cuda.current_stream(self.device)
+        if self.steps >= 2:
+            main.wait_event(self.ev_red[k])
+        self.steps += 1
+        if self.rows:
+            capi.norm_backward(capi.LAYERNORM, dy, self._x, self.mean, self.rstd, gamma, None, self.dx, None, None,
+                               buf, self.ws)
+        else:
+            buf.zero_()  # an empty shard contributes zeros
+        self.ev_bwd[k].record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.ev_bwd[k])
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+            capi.cast_from_f32(buf, self.dparams, stream=self.side)
+            self.ev_red[k].record(self.side)
+        return self.dx
+
+    def finish(self):
+        """Makes the current stream wait for the reductions still in flight and returns
+        (dgamma, dbeta) of the last step, summed over all ranks, in the parameter dtype."""
+        if self.side is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.side)
+        return self.dparams[: self.hidden], self.dparams[self.hidden:]
+
+    def last_sums_f32(self) -> torch.Tensor:
+        """The unrounded fp32 [dgamma | dbeta] of the last step (after finish(): summed over all
+        ranks)."""
+        if self.world == 1:
+            return self.dgb[0]
+        return self.dgb[(self.steps - 1) & 1]

@@ -204,6 +204,11 @@ int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean
 int fln_layernorm_backward_static(const void* dy, const void* x, const float* mean,
                                   const float* rstd, const void* gamma, void* dx, void* dgamma,
                                   void* dbeta, int64_t rows, int64_t cols, int dtype, void* stream);
+/* Lowers the size beyond which fln_layernorm_backward_static refuses a problem (never above
+ * FLN_STATIC_SCRATCH_BYTES; 0 restores that).  On a B200 no plan of the present launcher needs
+ * more than 14.5 MB (148 SMs x 512 threads x 24 columns x 8 bytes), so the refusal can only be
+ * seen by lowering the limit; tests do.  No counterpart in the reference. */
+void fln_set_static_scratch_limit(size_t bytes);
 
 /* dst[i] = (dtype) src[i] for n fp32 values: turns an all-reduced dgb_f32 buffer into
  * parameter-typed gradients.  No counterpart in the reference. */
@@ -292,11 +297,36 @@ void fln_set_sm_reserve(int sms);
  * No counterpart in the reference. */
 int fln_planner_selftest(void);
 
+/* Tuning hook: stages (tiles in flight) per CTA of the pipelined kernels; 0 = automatic (about
+ * 96 KB in flight per SM), >= 2 forces that many where they fit.  Query
+ * fln_backward_workspace_bytes again after changing it.  No counterpart in the reference. */
+void fln_set_stage_override(int stages);
+
 /* Reads and clears the device status word of the current device (synchronizes the device).
- * 0 = no kernel reported a problem; 1 = a pipelined kernel gave up waiting for a bulk copy
- * (its outputs are then incomplete); -1 = the status could not be read.  The reference has
- * no error reporting on its launch path (csrc/layernorm_cuda_kernel.cu:171,199). */
+ * 0 = no kernel reported a problem; otherwise a sum of
+ *   1  a pipelined kernel gave up waiting for a bulk copy (its outputs are incomplete),
+ *   2  the backward's grid barrier gave up waiting for the other CTAs (dgamma / dbeta of that
+ *      launch are stale; dx is complete),
+ *   4  the forward's tile counter did not add up at the end of a launch (two launches shared a
+ *      counter pair: more than 1024 pipelined forward launches in flight at once);
+ * -1 = the status could not be read.  Every exit path of the kernels -- the ones that gave up
+ * included -- leaves the grid barrier's word and the tile counter ready for the next launch or
+ * graph replay.  The reference has no error reporting on its launch path
+ * (csrc/layernorm_cuda_kernel.cu:171,199). */
 int fln_device_status(void);
+
+/* Every wait inside a kernel (for a bulk copy, at the grid barrier) gives up after this many
+ * nanoseconds of the GPU's global timer and reports through fln_device_status().  Default
+ * 1e9 (one second; 0 restores it).  Applies to the current device.  Tests lower it to make a
+ * wait run out quickly.  No counterpart in the reference. */
+int fln_set_wait_limit_ns(unsigned long long ns);
+
+/* Test hook, off by default, current device: bit 0 -- CTA 0 of a pipelined kernel arms the
+ * barrier of its first tile without issuing the copy, so its wait runs out (status 1);
+ * bit 1 -- the backward's grid barrier expects one CTA more than the grid has, so every CTA's
+ * wait runs out (status 2).  Nothing faults and nothing spins without bound: the kernels
+ * return through their ordinary give-up paths.  No counterpart in the reference. */
+int fln_set_test_fault(int bits);
 
 #ifdef __cplusplus
 }

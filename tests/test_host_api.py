@@ -113,6 +113,25 @@ def test_replace_layernorm_modules_shares_parameters():
     assert isinstance(model[2][0], FusedLayerNorm) and model[2][0].weight is None
 
 
+def test_layernorm_without_bias_is_constructible_and_replaceable():
+    """torch.nn.LayerNorm(d, bias=False): weight only.  The module takes the same keyword, the
+    module walker carries it over, and the rebound torch.nn.LayerNorm accepts it."""
+    m = FusedLayerNorm(8, bias=False)
+    assert m.weight is not None and m.bias is None
+    assert [k for k, _ in m.named_parameters()] == ["weight"]
+    m.weight.requires_grad_(False)  # a frozen weight and no bias: the inference test must not trip on None
+    model = nn.Sequential(nn.LayerNorm(8, bias=False))
+    w = model[0].weight
+    assert fused_layernorm.replace_layernorm_modules(model) == 1
+    assert model[0].weight is w and model[0].bias is None
+    assert set(model.state_dict()) == {"0.weight"}
+    fused_layernorm.replace_torch_layernorm()
+    try:
+        assert torch.nn.LayerNorm(8, bias=False).bias is None
+    finally:
+        fused_layernorm.restore_torch_layernorm()
+
+
 def test_operator_schemas_and_fake_tracing():
     ops = torch.ops.fused_layernorm
     for name in ["layernorm", "layernorm_gelu", "layernorm_fwd", "rmsnorm_fwd", "add_layernorm_fwd", "add_rmsnorm_fwd",
