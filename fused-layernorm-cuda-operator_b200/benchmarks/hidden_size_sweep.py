@@ -51,7 +51,11 @@ def main():
     ap.add_argument("--dtypes", default="bfloat16,float32")
     ap.add_argument("--mib", type=int, default=512, help="size of each [rows, hidden] tensor")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--path-override", type=int, default=0,
+                    help="fln_set_path_override: 0 automatic, 1 register kernels only, 2 pipeline wherever it fits")
+    ap.add_argument("--skip-torch", action="store_true")
     args = ap.parse_args()
+    capi.lib().fln_set_path_override(args.path_override)
     out = []
     for dn in args.dtypes.split(","):
         dt = getattr(torch, dn)
@@ -68,7 +72,7 @@ def main():
             ws = torch.empty(max(capi.backward_workspace_bytes(rows, cols, dt) // 4, 1), device="cuda")
             tf = loop_us(lambda: capi.layernorm_forward(x, g, b, y, mean, rstd, 1e-5))
             tb = loop_us(lambda: capi.layernorm_backward(dy, x, mean, rstd, g, dx, dg, db, ws))
-            tt = loop_us(lambda: F.layer_norm(x, (cols,), g, b, 1e-5))
+            tt = float('inf') if args.skip_torch else loop_us(lambda: F.layer_norm(x, (cols,), g, b, 1e-5))
             nb = rows * cols * es
             rec = {"dtype": dn, "rows": rows, "hidden": cols, "fwd_us": tf, "fwd_gbs": 2 * nb / tf / 1e3,
                    "bwd_us": tb, "bwd_gbs": 3 * nb / tb / 1e3, "torch_fwd_gbs": 2 * nb / tt / 1e3,

@@ -567,12 +567,15 @@ static int launch_bwd_k(const BwdParams& p, const BwdLaunch& L, cudaStream_t st)
   return FLN_OK;
 }
 
+// partial_rows_out != nullptr: stage 1 only -- the partial rows stay in the workspace, their
+// number is reported, and nothing is reduced (fln_norm_backward_partial)
 template <typename T, int KIND>
 static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void* workspace,
-                   size_t workspace_bytes, bool aligned, cudaStream_t st) {
+                   size_t workspace_bytes, bool aligned, cudaStream_t st, int64_t* partial_rows_out = nullptr) {
   constexpr int NR = KIND == FLN_LAYERNORM ? 2 : 1;
   constexpr int FULL = 16 / sizeof(T);
-  const bool want_params = dgamma != nullptr || dbeta != nullptr || dgb_f32 != nullptr;
+  const bool defer = partial_rows_out != nullptr;
+  const bool want_params = defer || dgamma != nullptr || dbeta != nullptr || dgb_f32 != nullptr;
   // large aligned problems: persistent bulk-async pipeline for stage 1
   const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
   const int64_t pipeP =
@@ -586,7 +589,7 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
       // a workspace of the full advertised size has one more 16-byte slot behind the
       // partial rows: the word the fused column reduce synchronises on
       const size_t sync_off = (need + 15) & ~(size_t)15;
-      if (workspace_bytes >= sync_off + 16) {
+      if (!defer && workspace_bytes >= sync_off + 16) {
         p.sync = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(workspace) + sync_off);
         p.dgb_f32 = dgb_f32;
         p.dgamma = dgamma;
@@ -599,6 +602,10 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
     const int rc = launch_bwd_pipeline(KIND, dt, p, st, &reduced);
     if (rc != FLN_PIPE_NOT_APPLICABLE) {
       if (rc != FLN_OK) return rc;
+      if (defer) {
+        *partial_rows_out = pipeP;
+        return FLN_OK;
+      }
       if (want_params && !reduced) {
         const int ncols = NR * p.cols;
         launch_colreduce<T>(p.partials, (int)pipeP, ncols, p.cols, dgb_f32, reinterpret_cast<T*>(dgamma),
@@ -647,6 +654,10 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
                               : launch_bwd_k<T, 1, KIND>(p, L, st);
     if (rc != FLN_OK) return rc;
   }
+  if (defer) {
+    *partial_rows_out = L.P;
+    return FLN_OK;
+  }
   if (want_params) {
     const int ncols = NR * p.cols;
     launch_colreduce<T>(p.partials, (int)L.P, ncols, p.cols, dgb_f32, reinterpret_cast<T*>(dgamma),
@@ -693,17 +704,21 @@ extern "C" size_t fln_backward_workspace_bytes(int64_t rows, int64_t cols, int d
   return 0;
 }
 
-extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean,
-                                 const float* rstd, const void* gamma, const void* dres_in,
-                                 void* dx, void* dgamma, void* dbeta, float* dgb_f32,
-                                 void* workspace, size_t workspace_bytes, int64_t rows,
-                                 int64_t cols, int dtype, void* stream) {
+static int norm_backward_impl(int kind, const void* dy, const void* x, const float* mean,
+                              const float* rstd, const void* gamma, const void* dres_in,
+                              void* dx, void* dgamma, void* dbeta, float* dgb_f32,
+                              void* workspace, size_t workspace_bytes, int64_t rows,
+                              int64_t cols, int dtype, void* stream, int64_t* partial_rows_out) {
   if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
   if (dtype != FLN_F32 && dtype != FLN_BF16 && dtype != FLN_F16) return FLN_ERR_DTYPE;
   if (kind == FLN_RMSNORM && dbeta != nullptr) return FLN_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (rows == 0) {
+    if (partial_rows_out != nullptr) {
+      *partial_rows_out = 0;  // nothing to sum
+      return FLN_OK;
+    }
     // an empty shard contributes zeros
     const size_t es = dtype == FLN_F32 ? 4 : 2;
     if (dgamma) cudaMemsetAsync(dgamma, 0, (size_t)cols * es, st);
@@ -715,7 +730,8 @@ extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const 
   if (dy == nullptr || x == nullptr || rstd == nullptr) return FLN_ERR_NULL;
   if (kind == FLN_LAYERNORM && mean == nullptr) return FLN_ERR_NULL;
   if (dres_in != nullptr && dx == nullptr) return FLN_ERR_NULL;
-  if (dx == nullptr && dgamma == nullptr && dbeta == nullptr && dgb_f32 == nullptr) return FLN_OK;
+  if (partial_rows_out == nullptr && dx == nullptr && dgamma == nullptr && dbeta == nullptr && dgb_f32 == nullptr)
+    return FLN_OK;
 
   BwdParams p;
   p.dy = dy;
@@ -745,13 +761,33 @@ extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const 
 #define FLN_RUN(T)                                                                         \
   (kind == FLN_LAYERNORM                                                                   \
        ? run_bwd<T, FLN_LAYERNORM>(p, dgamma, dbeta, dgb_f32, workspace, workspace_bytes,  \
-                                   aligned, st)                                            \
+                                   aligned, st, partial_rows_out)                          \
        : run_bwd<T, FLN_RMSNORM>(p, dgamma, dbeta, dgb_f32, workspace, workspace_bytes,    \
-                                 aligned, st))
+                                 aligned, st, partial_rows_out))
   if (dtype == FLN_F32) return FLN_RUN(float);
   if (dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
   return FLN_RUN(__half);
 #undef FLN_RUN
+}
+
+extern "C" int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean,
+                                 const float* rstd, const void* gamma, const void* dres_in,
+                                 void* dx, void* dgamma, void* dbeta, float* dgb_f32,
+                                 void* workspace, size_t workspace_bytes, int64_t rows,
+                                 int64_t cols, int dtype, void* stream) {
+  return norm_backward_impl(kind, dy, x, mean, rstd, gamma, dres_in, dx, dgamma, dbeta, dgb_f32, workspace,
+                            workspace_bytes, rows, cols, dtype, stream, nullptr);
+}
+
+extern "C" int fln_norm_backward_partial(int kind, const void* dy, const void* x, const float* mean,
+                                         const float* rstd, const void* gamma, const void* dres_in,
+                                         void* dx, void* workspace, size_t workspace_bytes,
+                                         int64_t rows, int64_t cols, int dtype, void* stream,
+                                         int64_t* partial_rows) {
+  if (partial_rows == nullptr || workspace == nullptr) return FLN_ERR_NULL;
+  *partial_rows = 0;
+  return norm_backward_impl(kind, dy, x, mean, rstd, gamma, dres_in, dx, nullptr, nullptr, nullptr, workspace,
+                            workspace_bytes, rows, cols, dtype, stream, partial_rows);
 }
 
 extern "C" int fln_layernorm_backward(const void* dy, const void* x, const float* mean,

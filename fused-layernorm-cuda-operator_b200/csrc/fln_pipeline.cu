@@ -50,10 +50,10 @@ static std::atomic<int> g_path_override{0};
 static std::atomic<int> g_stage_override{0};
 // every pipelined forward launch takes the next pair of g_tile_sched
 static std::atomic<unsigned int> g_sched_seq{0};
-// How long a wait inside a kernel may last, in nanoseconds of %globaltimer.  It travels in the
-// kernel parameters (constant bank): a wait that reads it from global memory pays a trip to L2
-// whenever its first probe fails, which in a memory-bound kernel is most of the time (the
-// backward at 16384 x 8192 bf16 took 205 instead of 130 us that way).
+// How long a wait inside a kernel may last, in nanoseconds.  It travels in the kernel parameters
+// (constant bank): a wait that reads it from global memory pays a trip to L2 whenever its first
+// probe fails, which in a memory-bound kernel is most of the time (the backward at 16384 x 8192
+// bf16 took 205 instead of 145 us that way).
 static std::atomic<unsigned long long> g_wait_limit_ns{1000ull * 1000ull * 1000ull};
 
 
@@ -215,7 +215,7 @@ PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
   PipePlan P = backward ? plan_bwd_pipeline(rows, cols, elem_bytes, false) : plan_pipeline(false, rows, cols, elem_bytes, 1);
   if (!pipeline_wanted(P, rows)) return false;
-  if (!backward && elem_bytes == 4 && cols <= 4096 && g_path_override.load(std::memory_order_relaxed) == 0) {
+  if (!backward && elem_bytes == 4 && cols <= 12288 && g_path_override.load(std::memory_order_relaxed) == 0) {
     // the fp32 LayerNorm forward of short exact rows goes to the register kernel (launch_fwd_pipeline)
     const Plan rp = make_plan(false, rows, cols, elem_bytes, true);
     if (!rp.generic && rp.vec == 4 && (int64_t)rp.K * rp.tpr * rp.vec == cols) return false;

@@ -92,18 +92,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 // Waits until the barrier's phase `parity` has completed, for at most about limit_ns.  The
-// common case -- the copy has landed or lands within a few probes -- reads no clock at all:
-// reading %globaltimer in every wait that does not succeed at once cost the bf16 backward at
-// 16384 x 8192 15 us of 130.  After 64 failed probes the wait is timed with the SM's cycle
-// counter, read once per 32 probes, against limit_ns * 2 cycles (the SM clock never exceeds
-// 2 GHz, so the wait lasts at least limit_ns and at most about 1.5 times that at the lowest
-// clocks seen under load); the outer loop also has an iteration cap.
+// common case -- the copy has landed or lands within a few probes -- reads no clock at all.
+// After 64 failed probes the wait is timed with the SM's cycle counter, read once per 32
+// probes, against limit_ns * 2 cycles (the SM clock never exceeds 2 GHz, so the wait lasts at
+// least limit_ns and at most about 1.5 times that at the lowest clocks seen under load); the
+// outer loop also has an iteration cap.  The limit arrives as a kernel parameter: fetching it
+// from global memory whenever a first probe failed put a trip to L2 in front of most rows.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
 #pragma unroll 1
   for (int it = 0; it < 64; ++it)
@@ -191,15 +186,19 @@ __device__ __forceinline__ void grid_arrive(unsigned long long* w) {
   __threadfence();
   atomicAdd(w, 1ull);
 }
+// Polls the word until `expect` CTAs of this launch have arrived, for at most about limit_ns
+// (timed like mbar_wait_bounded: SM cycle counter against limit_ns * 2 cycles, read once per 16
+// polls).
 __device__ __forceinline__ bool grid_wait(unsigned long long* w, unsigned long long token, unsigned int expect,
                                           unsigned long long limit_ns) {
-  const unsigned long long t0 = global_ns();
-  for (uint32_t it = 0; it < (1u << 28); ++it) {
+  const long long t0 = clock64();
+  const long long limit_cycles = (long long)(limit_ns << 1);
+  for (uint32_t it = 0; it < (1u << 30); ++it) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(w) : "memory");
     if ((v >> 24) == token && (unsigned int)(v & 0xfffull) == expect) return true;
-    if (global_ns() - t0 > limit_ns) return false;
-    __nanosleep(64);
+    if ((it & 15u) == 15u && clock64() - t0 > limit_cycles) return false;
+    __nanosleep(32);
   }
   return false;
 }

@@ -31,7 +31,7 @@ SYMBOLS = [
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
     "fln_planner_selftest", "fln_sum_rows_f32", "fln_set_stage_override", "fln_set_wait_limit_ns",
-    "fln_set_test_fault", "fln_set_static_scratch_limit",
+    "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -72,6 +72,7 @@ def lib() -> C.CDLL:
     L.fln_backward_workspace_bytes.argtypes = [i64, i64, i32]
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_norm_backward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
+    L.fln_norm_backward_partial.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp, C.POINTER(i64)]
     L.fln_cast_from_f32.argtypes = [vp, vp, i64, i32, vp]
     L.fln_sum_rows_f32.argtypes = [vp, i64, i64, vp, vp, i32, vp]
     L.fln_set_stage_override.restype = None
@@ -195,6 +196,19 @@ def norm_backward(kind, dy, x, mean, rstd, gamma, dres_in, dx, dgamma, dbeta, dg
     check(lib().fln_norm_backward(kind, ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dres_in),
                                   ptr(dx), ptr(dgamma), ptr(dbeta), ptr(dgb_f32), ptr(workspace), ws_bytes,
                                   rows, cols, dtype_code(x), stream_handle(stream)), "fln_norm_backward")
+
+
+def norm_backward_partial(kind, dy, x, mean, rstd, gamma, dres_in, dx, workspace, stream=None):
+    """Stage 1 only: dx and the unreduced partial sums.  Returns them as a view [P, NR * cols]
+    of `workspace` (fp32); add its rows with sum_rows_f32, on any stream."""
+    rows, cols = x.shape
+    n = C.c_int64(0)
+    ws_bytes = workspace.numel() * workspace.element_size()
+    check(lib().fln_norm_backward_partial(kind, ptr(dy), ptr(x), ptr(mean), ptr(rstd), ptr(gamma), ptr(dres_in), ptr(dx),
+                                          ptr(workspace), ws_bytes, rows, cols, dtype_code(x), stream_handle(stream),
+                                          C.byref(n)), "fln_norm_backward_partial")
+    nr = 2 if kind == LAYERNORM else 1
+    return workspace.view(torch.float32).reshape(-1)[: n.value * nr * cols].view(n.value, nr * cols)
 
 
 def layernorm_backward(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace, stream=None):

@@ -125,26 +125,27 @@ class ShardedLayerNorm:
 
 class ShardedLayerNormStep:
     """The training step of one rank, preallocated: LayerNorm forward + backward over this rank's
-    shard with the all-reduce of the parameter gradients off the critical path.
+    shard with the sums of the parameter gradients off the critical path.
 
         step = ShardedLayerNormStep(rows, hidden, torch.bfloat16)   # after init_process_group
         for batch in loader:
             y = step.forward(x, gamma, beta)           # current stream, no communication
-            dx = step.backward(dy, gamma)              # current stream; the reduction is queued
+            dx = step.backward(dy, gamma)              # current stream; the sums are queued
             ...
-        dgamma, dbeta = step.finish()                  # joins the reductions still in flight
+        dgamma, dbeta = step.finish()                  # joins the sums still in flight
 
-    The fp32 [dgamma | dbeta] sums of a step are all-reduced and rounded to the parameter dtype
-    on a side stream, behind an event that follows the backward; the stream the caller launches
-    on never waits for them (a training loop needs the parameter gradients at its optimizer
-    step, not before), so the collective overlaps the next forward.  Two fp32 buffers alternate;
-    before a buffer is written again the caller's stream waits for the event that marks its
-    previous reduction as finished, which by then lies a whole step in the past.  Everything is
-    launched through the C ABI on buffers allocated here once, so a step allocates nothing.
-
-    With one rank (or no process group) there is nothing to reduce: the backward writes dgamma
-    and dbeta itself.  No kernel of this class waits on a peer; the only cross-rank
-    synchronization is the collective.
+    The backward launched on the caller's stream is stage 1 only (dx and the per-CTA partial sums
+    of dgamma / dbeta): its kernel ends without a grid-wide barrier, so whatever the caller
+    launches next starts while its last CTAs finish.  The column sum of the partial rows, the
+    all-reduce of the fp32 [dgamma | dbeta] over the ranks (when there are several) and the
+    rounding to the parameter dtype run on a side stream, behind an event that follows the
+    backward; the caller's stream never waits for them (a training loop needs the parameter
+    gradients at its optimizer step, not before), so they overlap the next forward.  Two sets of
+    buffers alternate; before a set is written again the caller's stream waits for the event that
+    marks its previous sums as finished, which by then lies a whole step in the past.
+    Everything is launched through the C ABI on buffers allocated here once, so a step allocates
+    nothing.  No kernel of this class waits on a peer; the only cross-rank synchronization is
+    the collective.
     """
 
     def __init__(self, rows: int, hidden: int, dtype=torch.bfloat16, eps: float = 1e-5, group=None,
@@ -164,15 +165,16 @@ class ShardedLayerNormStep:
         self.dgb = [torch.zeros(2 * hidden, dtype=torch.float32, device=d) for _ in range(2)]
         self.dparams = torch.zeros(2 * hidden, dtype=dtype, device=d)
         ws = capi.backward_workspace_bytes(rows, hidden, dtype)
-        self.ws = torch.empty(max(ws // 4, 1), dtype=torch.float32, device=d)
-        self.side = torch.cuda.Stream(d) if self.world > 1 else None
+        self.ws = [torch.empty(max(ws // 4, 1), dtype=torch.float32, device=d) for _ in range(2)]
+        self.side = torch.cuda.Stream(d)
         self.ev_bwd = [torch.cuda.Event() for _ in range(2)]
         self.ev_red = [torch.cuda.Event() for _ in range(2)]
         self.steps = 0
         self._x = None
-        # kernels of this library per step: forward, backward (the column sums are reduced in
-        # its own tail), and with more than one rank the rounding of the all-reduced sums
-        self.launches_per_step = 2 + (1 if self.world > 1 else 0)
+        # kernels of this library per step: forward, backward stage 1, the column sum of the
+        # partial rows (which also rounds when there is one rank), and with more than one rank
+        # the rounding of the all-reduced sums
+        self.launches_per_step = 3 + (1 if self.world > 1 else 0)
 
     def forward(self, x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor]) -> torch.Tensor:
         if x.shape != (self.rows, self.hidden) or x.dtype != self.dtype:
@@ -188,42 +190,38 @@ class ShardedLayerNormStep:
             raise RuntimeError("backward() before forward()")
         if dy.shape != self._x.shape or dy.dtype != self.dtype:
             raise ValueError(f"dy must match x: {tuple(self._x.shape)} {self.dtype}")
-        h = self.hidden
-        if self.world == 1:
-            if self.rows:
-                capi.norm_backward(capi.LAYERNORM, dy, self._x, self.mean, self.rstd, gamma, None, self.dx,
-                                   self.dparams[:h], self.dparams[h:], self.dgb[0], self.ws)
-            self.steps += 1
-            return self.dx
         k = self.steps & 1
         buf = self.dgb[k]
         main = torch.cuda.current_stream(self.device)
         if self.steps >= 2:
-            main.wait_event(self.ev_red[k])
+            main.wait_event(self.ev_red[k])  # buffer set k is free again
         self.steps += 1
+        partial = None
         if self.rows:
-            capi.norm_backward(capi.LAYERNORM, dy, self._x, self.mean, self.rstd, gamma, None, self.dx, None, None,
-                               buf, self.ws)
-        else:
-            buf.zero_()  # an empty shard contributes zeros
+            partial = capi.norm_backward_partial(capi.LAYERNORM, dy, self._x, self.mean, self.rstd, gamma, None,
+                                                 self.dx, self.ws[k])
         self.ev_bwd[k].record(main)
         with torch.cuda.stream(self.side):
             self.side.wait_event(self.ev_bwd[k])
-            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
-            capi.cast_from_f32(buf, self.dparams, stream=self.side)
+            if partial is not None and partial.shape[0] > 0:
+                capi.sum_rows_f32(partial, buf, self.dparams if self.world == 1 else None, stream=self.side)
+            else:
+                buf.zero_()  # an empty shard contributes zeros
+                if self.world == 1:
+                    self.dparams.zero_()
+            if self.world > 1:
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+                capi.cast_from_f32(buf, self.dparams, stream=self.side)
             self.ev_red[k].record(self.side)
         return self.dx
 
     def finish(self):
-        """Makes the current stream wait for the reductions still in flight and returns
-        (dgamma, dbeta) of the last step, summed over all ranks, in the parameter dtype."""
-        if self.side is not None:
-            torch.cuda.current_stream(self.device).wait_stream(self.side)
+        """Makes the current stream wait for the sums still in flight and returns (dgamma,
+        dbeta) of the last step, summed over all ranks, in the parameter dtype."""
+        torch.cuda.current_stream(self.device).wait_stream(self.side)
         return self.dparams[: self.hidden], self.dparams[self.hidden:]
 
     def last_sums_f32(self) -> torch.Tensor:
         """The unrounded fp32 [dgamma | dbeta] of the last step (after finish(): summed over all
         ranks)."""
-        if self.world == 1:
-            return self.dgb[0]
         return self.dgb[(self.steps - 1) & 1]

@@ -183,6 +183,21 @@ int fln_norm_backward(int kind, const void* dy, const void* x, const float* mean
                       size_t workspace_bytes, int64_t rows, int64_t cols, int dtype,
                       void* stream);
 
+/* Stage 1 of fln_norm_backward on its own: dx, and the per-CTA partial sums of dgamma / dbeta
+ * left unreduced in `workspace` as an fp32 matrix [*partial_rows, NR * cols] (NR = 2 for
+ * LayerNorm: dgamma sums then dbeta sums; 1 for RMSNorm), row pitch NR * cols.  The caller adds
+ * the rows with fln_sum_rows_f32 when and where it likes -- typically on another stream, so
+ * that the kernel after the backward does not wait for the column sums (they are needed at the
+ * optimizer step, not before).  The kernel of this entry point ends without a grid-wide barrier,
+ * so the next kernel's CTAs start while its last CTAs finish: 123 instead of 133 us per call at
+ * 16384 x 8192 bf16, back to back.  The sums are added in a fixed order either way.
+ * *partial_rows is 0 for rows == 0.  No counterpart in the reference (its backward is declared
+ * in csrc/layernorm.h:24-32 and defined nowhere). */
+int fln_norm_backward_partial(int kind, const void* dy, const void* x, const float* mean,
+                              const float* rstd, const void* gamma, const void* dres_in, void* dx,
+                              void* workspace, size_t workspace_bytes, int64_t rows, int64_t cols,
+                              int dtype, void* stream, int64_t* partial_rows);
+
 /* LayerNorm backward that allocates nothing and asks the caller for no scratch either.
  * It has no counterpart in the reference.  It exists for hosts that must not allocate device
  * memory once they are running: runtimes with a fixed memory plan (all device memory is
@@ -315,10 +330,11 @@ void fln_set_stage_override(int stages);
  * (csrc/layernorm_cuda_kernel.cu:171,199). */
 int fln_device_status(void);
 
-/* Every wait inside a kernel (for a bulk copy, at the grid barrier) gives up after this many
- * nanoseconds of the GPU's global timer and reports through fln_device_status().  Default
- * 1e9 (one second; 0 restores it).  Applies to the current device.  Tests lower it to make a
- * wait run out quickly.  No counterpart in the reference. */
+/* Every wait inside a kernel (for a bulk copy, at the grid barrier) gives up after about this
+ * many nanoseconds (counted in SM cycles at 2 per nanosecond, so up to 1.5 times longer at low
+ * clocks) and reports through fln_device_status().  Default 1e9 (one second; 0 restores it).
+ * Process-wide; launches recorded into a CUDA graph keep the limit they were recorded with.
+ * Tests lower it to make a wait run out quickly.  No counterpart in the reference. */
 int fln_set_wait_limit_ns(unsigned long long ns);
 
 /* Test hook, off by default, current device: bit 0 -- CTA 0 of a pipelined kernel arms the
