@@ -469,6 +469,24 @@ def run_ours(args):
         time.sleep(0.25)
     plain = timed_passes(torch, dist, step, x, dy, gamma, beta, K, max(args.passes, 1), False)
     phased = timed_passes(torch, dist, step, x, dy, gamma, beta, K, max(min(args.passes, 3), 1), True)
+    # the two kernels alone, back to back (K launches between two events): consecutive launches
+    # overlap their tails and heads, which event-separated launches cannot
+    def alone_ms(fn):
+        for _ in range(3):
+            fn()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            fn()
+        step.finish()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / K
+    fwd_alone, bwd_alone = max_over_ranks(torch, dist, [alone_ms(lambda: step.forward(x, gamma, beta)),
+                                                        alone_ms(lambda: step.backward(dy, gamma))])
     clocks = sampler.stop() if rank == 0 else None
     # every pass: max over ranks; then the median pass is the reported one
     per_step = max_over_ranks(torch, dist, [p[0] / K for p in plain])
@@ -578,11 +596,15 @@ def run_ours(args):
                                "is a third, small launch on a side stream)",
                      "bound": "hbm", "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
                      "traffic": traffic["bytes"], "traffic_source": traffic["source"], "peak_source": peak_src,
-                     "algorithmic_bytes": bwd_b, "avg_ms": bwd_ms,
-                     "timing": "CUDA events around every launch in further passes of the same K steps "
-                               f"({instrumented_ms:.4f} ms/step with those events in the stream)"},
+                     "algorithmic_bytes": bwd_b, "avg_ms": bwd_ms, "avg_ms_back_to_back": bwd_alone,
+                     "frac_back_to_back": bwd_b / (bwd_alone * 1e-3) / 1e9 / peak,
+                     "timing": "avg_ms: CUDA events around every launch in further passes of the same K steps "
+                               f"({instrumented_ms:.4f} ms/step with those events in the stream); "
+                               "avg_ms_back_to_back: K launches of this kernel alone between two events"},
         "roofline_forward": {"kernel": "norm_fwd_pipe_kernel", "bound": "hbm", "achieved": fwd_gbs, "peak": peak,
-                             "unit": "GB/s", "frac": fwd_gbs / peak, "algorithmic_bytes": fwd_b, "avg_ms": fwd_ms},
+                             "unit": "GB/s", "frac": fwd_gbs / peak, "algorithmic_bytes": fwd_b, "avg_ms": fwd_ms,
+                             "avg_ms_back_to_back": fwd_alone,
+                             "frac_back_to_back": fwd_b / (fwd_alone * 1e-3) / 1e9 / peak},
         "clocks": clocks, "gpu_launches": K * launches_per_step,
     }
     if parity:

@@ -35,6 +35,12 @@ SEQ_LENS = [128, 256, 512, 1024]
 DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
 SUBSET_MODELS = {"BERT-Base", "GPT-2 XL", "GPT-3 Large", "GPT-3 XXL", "GPT-3 175B"}
 SUBSET_SHAPES = [(1, 128), (8, 512), (32, 1024)]
+# the columns of the reference's result record (benchmarks/benchmark_layernorm.py:218-237), in
+# its order; this script's records start with them and add fused_forward_gbs
+REFERENCE_COLUMNS = ["model_name", "batch_size", "seq_len", "hidden_size", "total_seq_len", "dtype",
+                     "pytorch_forward_ms", "fused_forward_ms", "forward_speedup", "pytorch_backward_ms",
+                     "fused_backward_ms", "backward_speedup", "total_speedup", "pytorch_memory_mb", "fused_memory_mb",
+                     "memory_reduction", "max_diff", "timestamp"]
 
 
 def loop_ms(fn, warmup, iters):

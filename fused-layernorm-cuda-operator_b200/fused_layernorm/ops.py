@@ -196,3 +196,41 @@ def _addrms_backward(ctx, gy, gsum, _grstd):
 
 
 torch.library.register_autograd("fused_layernorm::add_rmsnorm_fwd", _addrms_backward, setup_context=_addrms_setup)
+
+
+# ------------------------------------------------------------------ convenience operators
+# Value-only forms of the operators above, under the names a caller would look for first.
+# They are composites (CompositeImplicitAutograd): under tracing they decompose into the
+# *_fwd / norm_fp8 operators, whose fakes and autograd formulas then apply, so they need none
+# of their own.
+_frag = torch.library.Library("fused_layernorm", "FRAGMENT")
+_frag.define("rmsnorm(Tensor input, Tensor? gamma, float epsilon) -> Tensor")
+_frag.define("add_layernorm(Tensor input, Tensor residual, Tensor? gamma, Tensor? beta, float epsilon) -> (Tensor, Tensor)")
+_frag.define("add_rmsnorm(Tensor input, Tensor residual, Tensor? gamma, float epsilon) -> (Tensor, Tensor)")
+_frag.define("add_rmsnorm_fp8(Tensor input, Tensor residual, Tensor? gamma, float epsilon) -> (Tensor, Tensor, Tensor)")
+
+
+def _rmsnorm(input, gamma, epsilon):
+    return ops.rmsnorm_fwd(input, gamma, epsilon)[0]
+
+
+def _add_layernorm(input, residual, gamma, beta, epsilon):
+    y, s, _mean, _rstd = ops.add_layernorm_fwd(input, residual, gamma, beta, epsilon)
+    return y, s
+
+
+def _add_rmsnorm(input, residual, gamma, epsilon):
+    y, s, _rstd = ops.add_rmsnorm_fwd(input, residual, gamma, epsilon)
+    return y, s
+
+
+def _add_rmsnorm_fp8(input, residual, gamma, epsilon):
+    """(q, sum, scale): e4m3 output with the per-tensor scale 448 / amax computed on the device."""
+    q, s, scale, _mean, _rstd = ops.norm_fp8(RMSNORM, input, residual, gamma, None, epsilon)
+    return q, s, scale
+
+
+_frag.impl("rmsnorm", _rmsnorm, "CompositeImplicitAutograd")
+_frag.impl("add_layernorm", _add_layernorm, "CompositeImplicitAutograd")
+_frag.impl("add_rmsnorm", _add_rmsnorm, "CompositeImplicitAutograd")
+_frag.impl("add_rmsnorm_fp8", _add_rmsnorm_fp8, "CompositeImplicitAutograd")

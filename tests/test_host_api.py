@@ -160,6 +160,23 @@ def test_operator_schemas_and_fake_tracing():
     assert dgb.shape == (64,) and dgb.dtype == torch.float32
 
 
+def test_value_only_operators_decompose_into_the_registered_forms():
+    """rmsnorm, add_layernorm, add_rmsnorm, add_rmsnorm_fp8 are registered operators; on meta
+    tensors they run through the fakes of the operators they are made of."""
+    ops = torch.ops.fused_layernorm
+    for name in ["rmsnorm", "add_layernorm", "add_rmsnorm", "add_rmsnorm_fp8"]:
+        assert hasattr(ops, name)
+    x = torch.empty(6, 32, device="meta", dtype=torch.bfloat16)
+    w = torch.empty(32, device="meta", dtype=torch.bfloat16)
+    assert ops.rmsnorm(x, w, 1e-6).shape == (6, 32)
+    y, s = ops.add_layernorm(x, x, w, w, 1e-5)
+    assert y.shape == s.shape == (6, 32)
+    y, s = ops.add_rmsnorm(x, x, w, 1e-6)
+    assert y.dtype == torch.bfloat16 and s.shape == (6, 32)
+    q, s, scale = ops.add_rmsnorm_fp8(x, x, w, 1e-6)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (6, 32) and scale.shape == (1,)
+
+
 def test_autograd_graph_is_built_on_fake_tensors():
     from torch._subclasses.fake_tensor import FakeTensorMode
     ops = torch.ops.fused_layernorm
