@@ -31,7 +31,7 @@ SYMBOLS = [
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
     "fln_planner_selftest", "fln_sum_rows_f32", "fln_set_stage_override", "fln_set_wait_limit_ns",
-    "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial",
+    "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial", "fln_dropout_add_norm_forward", "fln_dropout_backward",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -73,6 +73,9 @@ def lib() -> C.CDLL:
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_norm_backward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
     L.fln_norm_backward_partial.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp, C.POINTER(i64)]
+    u64 = C.c_ulonglong
+    L.fln_dropout_add_norm_forward.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, f32, u64, u64, vp]
+    L.fln_dropout_backward.argtypes = [vp, vp, vp, i64, i64, i32, f32, u64, u64, vp]
     L.fln_cast_from_f32.argtypes = [vp, vp, i64, i32, vp]
     L.fln_sum_rows_f32.argtypes = [vp, i64, i64, vp, vp, i32, vp]
     L.fln_set_stage_override.restype = None
@@ -184,6 +187,21 @@ def norm_forward_mxfp8(kind, x, residual, gamma, beta, q, block_scale, sum_out, 
     check(lib().fln_norm_forward_mxfp8(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q), ptr(block_scale),
                                        ptr(sum_out), ptr(mean), ptr(rstd), ptr(amax_out), rows, cols, dtype_code(x),
                                        eps, stream_handle(stream)), "fln_norm_forward_mxfp8")
+
+
+def dropout_add_norm_forward(kind, x, residual, gamma, beta, y, sum_out, mean, rstd, keep_bits, eps, p, seed, offset,
+                             stream=None):
+    """y = norm(dropout(x, p) + residual); keep_bits (uint8 [rows * cols / 8], optional) receives the mask."""
+    rows, cols = x.shape
+    check(lib().fln_dropout_add_norm_forward(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(y), ptr(sum_out),
+                                             ptr(mean), ptr(rstd), ptr(keep_bits), rows, cols, dtype_code(x), eps, p,
+                                             seed, offset, stream_handle(stream)), "fln_dropout_add_norm_forward")
+
+
+def dropout_backward(d_sum, keep_bits, d_x, p, seed, offset, stream=None):
+    rows, cols = d_sum.shape
+    check(lib().fln_dropout_backward(ptr(d_sum), ptr(keep_bits), ptr(d_x), rows, cols, dtype_code(d_sum), p, seed,
+                                     offset, stream_handle(stream)), "fln_dropout_backward")
 
 
 def backward_workspace_bytes(rows, cols, dtype) -> int:

@@ -234,3 +234,88 @@ _frag.impl("rmsnorm", _rmsnorm, "CompositeImplicitAutograd")
 _frag.impl("add_layernorm", _add_layernorm, "CompositeImplicitAutograd")
 _frag.impl("add_rmsnorm", _add_rmsnorm, "CompositeImplicitAutograd")
 _frag.impl("add_rmsnorm_fp8", _add_rmsnorm_fp8, "CompositeImplicitAutograd")
+
+
+# ----------------------------------------------------- fused dropout -> add -> norm (C ABI)
+# These two operators are defined here, in Python, on top of the C ABI (the allocation is
+# torch's, the launch goes through ctypes on the current stream); the kernels are
+# fln_dropout_add_norm_forward / fln_dropout_backward.
+from typing import Optional, Tuple  # noqa: E402
+
+from . import _capi  # noqa: E402
+
+
+@torch.library.custom_op("fused_layernorm::dropout_add_norm_fwd", mutates_args=())
+def dropout_add_norm_fwd(kind: int, input: torch.Tensor, residual: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
+                         beta: Optional[torch.Tensor], p: float, epsilon: float, seed: int,
+                         offset: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(y, sum, mean, rstd, keep_bits) of y = norm(dropout(input, p) + residual); mean is empty for
+    RMSNorm; keep_bits is uint8 [rows * cols / 8]."""
+    if input.dim() != 2 or not input.is_cuda:
+        raise RuntimeError("dropout_add_norm_fwd expects a 2-D CUDA tensor")
+    x = input.contiguous()
+    res = residual.contiguous() if residual is not None else None
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    s = torch.empty_like(x)
+    mean = x.new_empty((rows if kind == LAYERNORM else 0,), dtype=torch.float32)
+    rstd = x.new_empty((rows,), dtype=torch.float32)
+    bits = x.new_empty((rows * cols // 8,), dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        _capi.dropout_add_norm_forward(kind, x, res, gamma, beta, y, s, mean if kind == LAYERNORM else None, rstd, bits,
+                                       epsilon, p, seed, offset)
+    return y, s, mean, rstd, bits
+
+
+@dropout_add_norm_fwd.register_fake
+def _(kind, input, residual, gamma, beta, p, epsilon, seed, offset):
+    e = lambda: torch.empty_like(input, memory_format=torch.contiguous_format)
+    rows, cols = input.shape
+    return (e(), e(), input.new_empty((rows if kind == LAYERNORM else 0,), dtype=torch.float32), _stat(input),
+            input.new_empty((rows * cols // 8,), dtype=torch.uint8))
+
+
+@torch.library.custom_op("fused_layernorm::dropout_bwd", mutates_args=())
+def dropout_bwd(d_sum: torch.Tensor, keep_bits: torch.Tensor, p: float) -> torch.Tensor:
+    """Gradient of dropout's input from the gradient of its output and the stored keep bits."""
+    g = d_sum.contiguous()
+    out = torch.empty_like(g)
+    with torch.cuda.device(g.device):
+        _capi.dropout_backward(g, keep_bits, out, p, 0, 0)
+    return out
+
+
+@dropout_bwd.register_fake
+def _(d_sum, keep_bits, p):
+    return torch.empty_like(d_sum, memory_format=torch.contiguous_format)
+
+
+def _dan_setup(ctx, inputs, output):
+    kind, _input, residual, gamma, beta, p, _eps, _seed, _offset = inputs
+    _y, s, mean, rstd, bits = output
+    ctx.save_for_backward(s, gamma, mean, rstd, bits)
+    ctx.kind, ctx.p = kind, p
+    ctx.has_beta = beta is not None
+    ctx.has_res = residual is not None
+    ctx.set_materialize_grads(False)
+
+
+def _dan_backward(ctx, gy, gsum, _gmean, _grstd, _gbits):
+    s, gamma, mean, rstd, bits = ctx.saved_tensors
+    need = ctx.needs_input_grad  # kind, input, residual, gamma, beta, ...
+    want_ds = need[1] or need[2]
+    dgamma = dbeta = None
+    if gy is None:
+        ds = gsum
+    elif ctx.kind == LAYERNORM:
+        ds, dgamma, dbeta = ops.layernorm_bwd(gy, s, mean, rstd, gamma, gsum if want_ds else None, want_ds,
+                                              need[3] and gamma is not None, need[4] and ctx.has_beta)
+    else:
+        ds, dgamma = ops.rmsnorm_bwd(gy, s, rstd, gamma, gsum if want_ds else None, want_ds, need[3] and gamma is not None)
+    ds = _none_if_empty(ds)
+    dx = ops.dropout_bwd(ds, bits, ctx.p) if (need[1] and ds is not None) else None
+    return (None, dx, ds if (need[2] and ctx.has_res) else None, _none_if_empty(dgamma), _none_if_empty(dbeta),
+            None, None, None, None)
+
+
+torch.library.register_autograd("fused_layernorm::dropout_add_norm_fwd", _dan_backward, setup_context=_dan_setup)

@@ -67,6 +67,36 @@ def fused_add_rms_norm(input: torch.Tensor, residual: torch.Tensor, weight: Opti
     return y.reshape(input.shape), s.reshape(input.shape)
 
 
+_dropout_calls = 0
+
+
+def fused_dropout_add_layer_norm(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                                 weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                                 p: float = 0.1, eps: float = 1e-5, training: bool = True, rms: bool = False,
+                                 seed: Optional[int] = None, offset: Optional[int] = None):
+    """(norm(dropout(input, p) + residual), dropout(input, p) + residual) in one pass over HBM:
+    the head of a pre-norm transformer block (differentiable in input, residual, weight, bias; a
+    gradient arriving on the returned sum is added in).  `rms=True` selects RMSNorm.  With
+    training=False (or p == 0) nothing is dropped.  The mask is the Philox4x32-10 mask of
+    (seed, offset); by default seed is torch's CUDA seed and offset counts the calls of this
+    function, so torch.manual_seed makes a run reproducible.  Needs a last dimension that is a
+    multiple of 8 and at most 16384."""
+    global _dropout_calls
+    _require_cuda(input)
+    if not training:
+        p = 0.0
+    if seed is None:
+        seed = torch.cuda.initial_seed() & 0xffffffffffffffff
+    if offset is None:
+        offset = _dropout_calls
+        _dropout_calls += 1
+    kind = _ops.RMSNORM if rms else _ops.LAYERNORM
+    res = _flat(residual) if residual is not None else None
+    y, s, _mean, _rstd, _bits = _t.dropout_add_norm_fwd(kind, _flat(input), res, weight, None if rms else bias, float(p),
+                                                        float(eps), int(seed), int(offset))
+    return y.reshape(input.shape), s.reshape(input.shape)
+
+
 def fused_add_rms_norm_fp8(input: torch.Tensor, residual: Optional[torch.Tensor] = None,
                            weight: Optional[torch.Tensor] = None, eps: float = 1e-6):
     """(q, sum, scale): q = rms_norm(input + residual) quantized to float8_e4m3fn with the

@@ -238,6 +238,34 @@ int fln_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, void* s
 int fln_sum_rows_f32(const float* rows_in, int64_t n_rows, int64_t ncols, float* out_f32,
                      void* out_cast, int dtype, void* stream);
 
+/* Fused dropout -> residual add -> LayerNorm / RMSNorm forward: the step in front of the
+ * normalization in a pre-norm block, in one pass.
+ *   d = dropout(x, p): kept elements times 1 / (1 - p'), rounded to the I/O type
+ *   s = d + residual (rounded to the I/O type, written to sum_out; residual may be NULL)
+ *   y = norm(s) * gamma + beta        (same conventions as fln_norm_forward)
+ * The mask comes from Philox4x32-10 and is a pure function of (seed, offset, element index):
+ * one 128-bit output per group of 8 consecutive elements of the flattened matrix, 16 bits per
+ * element, counter = {group lo, group hi, offset lo, offset hi}, key = {seed lo, seed hi}; an
+ * element is kept iff its 16 bits >= round(p * 65536), so the drop probability is
+ * p' = round(p * 65536) / 65536 and 0 <= p < 1.
+ *   keep_bits  [rows * cols / 8] bytes or NULL: bit j of byte g = element 8 g + j was kept
+ * cols must be a multiple of 8 and at most 16384, every pointer 16-byte aligned, otherwise
+ * FLN_ERR_UNSUPPORTED.  The gradient of the block is fln_norm_backward on (dy, s) -- its dx is
+ * the gradient of s and of the residual -- followed by fln_dropout_backward for x.
+ * No counterpart in the reference. */
+int fln_dropout_add_norm_forward(int kind, const void* x, const void* residual, const void* gamma,
+                                 const void* beta, void* y, void* sum_out, float* mean, float* rstd,
+                                 unsigned char* keep_bits, int64_t rows, int64_t cols, int dtype,
+                                 float eps, float p, unsigned long long seed, unsigned long long offset,
+                                 void* stream);
+
+/* d_x = d_sum / (1 - p') where the element was kept, 0 where it was dropped.  The mask is read
+ * from keep_bits (as fln_dropout_add_norm_forward wrote it) or, with keep_bits == NULL,
+ * regenerated from (p, seed, offset).  d_x may be d_sum.  No counterpart in the reference. */
+int fln_dropout_backward(const void* d_sum, const unsigned char* keep_bits, void* d_x, int64_t rows,
+                         int64_t cols, int dtype, float p, unsigned long long seed,
+                         unsigned long long offset, void* stream);
+
 /* ----------------------------------------------------------------------------------
  * CUDA-graph launch path for latency-bound shapes
  * -------------------------------------------------------------------------------- */

@@ -331,3 +331,53 @@ API void ref_g2_layernorm_f32(const float* x, const float* gamma, const float* b
     }
   }
 }
+
+/* ------------------------------------------------------------------ dropout (counter-based) */
+
+/*
+ * Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3",
+ * SC'11), restated from the published algorithm: ten rounds of
+ *   (hi0, lo0) = M0 * c0, (hi1, lo1) = M1 * c2,  c' = {hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0}
+ * with the key bumped by the Weyl constants after every round.  The reference project has no
+ * dropout; this is the generator behind fln_dropout_add_norm_forward, pinned by the published
+ * known-answer vectors in tests/test_oracle_golden.py.
+ */
+API void oracle_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+  uint32_t c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1, n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1,
+                   n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+/* keep bits of `groups` groups of 8 elements: group g uses counter {g lo, g hi, offset lo,
+ * offset hi}, key {seed lo, seed hi}; element j keeps iff its 16 bits (word j / 2, half j % 2)
+ * are >= threshold. */
+API void oracle_dropout_keep_bits(uint64_t seed, uint64_t offset, uint32_t threshold, int64_t groups, uint8_t* bits) {
+  const uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+  for (int64_t g = 0; g < groups; ++g) {
+    const uint32_t ctr[4] = {(uint32_t)g, (uint32_t)((uint64_t)g >> 32), (uint32_t)offset, (uint32_t)(offset >> 32)};
+    uint32_t w[4];
+    oracle_philox4x32_10(ctr, key, w);
+    uint8_t m = 0;
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t v = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+      if (threshold == 0 || v >= threshold) m |= (uint8_t)(1u << j);
+    }
+    bits[g] = m;
+  }
+}
+
+/* out[i] = round_to_dt(x[i] * scale) where bit i is set, 0 elsewhere (forward and backward of
+ * dropout are the same map) */
+API void oracle_dropout_apply(const void* x, const uint8_t* bits, void* out, int64_t n, int dt, float scale) {
+  for (int64_t i = 0; i < n; ++i) {
+    const int keep = (bits[i >> 3] >> (i & 7)) & 1;
+    store_el(out, i, dt, keep ? (float)load_el(x, i, dt) * scale : 0.0f);
+  }
+}

@@ -55,6 +55,9 @@ def lib() -> C.CDLL:
         L.oracle_convert_from_f32.argtypes = [f32p, vp, i64, i32]
         L.oracle_convert_to_f32.argtypes = [vp, f32p, i64, i32]
         L.oracle_e4m3_encode.argtypes = [f32p, vp, i64]
+        L.oracle_philox4x32_10.argtypes = [vp, vp, vp]
+        L.oracle_dropout_keep_bits.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, i64, vp]
+        L.oracle_dropout_apply.argtypes = [vp, vp, vp, i64, i32, C.c_float]
         _lib = L
     return _lib
 
@@ -260,3 +263,36 @@ def mismatch_16(a, b, abs_floor=1e-5):
     (e.g. GELU of a large negative input) a bound in ulps of the tiny result is meaningless."""
     ulp = ulp_distance_16(a, b)
     return (ulp > 1) & ((a.float() - b.float()).abs() > abs_floor)
+
+
+def philox4x32_10(ctr, key):
+    """One block of Philox4x32-10: ctr (4 uint32), key (2 uint32) -> 4 uint32."""
+    c = np.asarray(ctr, dtype=np.uint32)
+    k = np.asarray(key, dtype=np.uint32)
+    out = np.zeros(4, dtype=np.uint32)
+    lib().oracle_philox4x32_10(c.ctypes.data_as(C.c_void_p), k.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def dropout_threshold(p: float):
+    """(threshold, scale) the library derives from p: drop iff 16 random bits < threshold."""
+    thr = min(int(p * 65536.0 + 0.5), 65535)
+    return thr, float(np.float32(65536.0 / (65536.0 - thr)))
+
+
+def dropout_keep_bits(seed: int, offset: int, p: float, n_elements: int):
+    """uint8 [n_elements / 8]: bit j of byte g = element 8 g + j is kept."""
+    assert n_elements % 8 == 0
+    bits = torch.zeros(n_elements // 8, dtype=torch.uint8)
+    thr, _ = dropout_threshold(p)
+    lib().oracle_dropout_keep_bits(seed, offset, thr, n_elements // 8, _ptr(bits))
+    return bits
+
+
+def dropout_apply(x, bits, p: float):
+    """round(x / (1 - p')) where kept, 0 elsewhere, in the dtype of x (forward and backward alike)."""
+    x = _c(x)
+    out = torch.empty_like(x)
+    _, scale = dropout_threshold(p)
+    lib().oracle_dropout_apply(_ptr(x), _ptr(bits), _ptr(out), x.numel(), DT[x.dtype], scale)
+    return out

@@ -161,3 +161,25 @@ def test_mxfp8_quantizer_matches_torch_composition():
     # the largest element of every block lands in [256, 512) before saturation: top binade
     top = (blocks / scale[..., None]).abs().amax(-1)[amax > 0]
     assert bool(((top >= 256) & (top < 512)).all())
+
+
+def test_philox_known_answers_and_keep_rate():
+    """The generator behind the fused dropout: Philox4x32-10 against the known-answer vectors
+    published with the algorithm (Random123 kat_vectors: zero, all-ones and pi-digits inputs),
+    and the keep rate of the mask derived from it."""
+    assert [hex(v) for v in O.philox4x32_10([0, 0, 0, 0], [0, 0])] == ["0x6627e8d5", "0xe169c58d", "0xbc57ac4c", "0x9b00dbd8"]
+    assert [hex(v) for v in O.philox4x32_10([0xffffffff] * 4, [0xffffffff] * 2)] == \
+        ["0x408f276d", "0x41c83b0e", "0xa20bc7c6", "0x6d5451fd"]
+    assert [hex(v) for v in O.philox4x32_10([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0])] == \
+        ["0xd16cfe09", "0x94fdcceb", "0x5001e420", "0x24126ea1"]
+    n = 1 << 20
+    for p in (0.0, 0.1, 0.5):
+        bits = O.dropout_keep_bits(99, 7, p, n)
+        kept = int(torch.tensor(np.unpackbits(bits.numpy())).sum())
+        assert abs(kept / n - (1 - p)) < 4e-3
+    assert not torch.equal(O.dropout_keep_bits(99, 7, 0.5, n), O.dropout_keep_bits(99, 8, 0.5, n))  # the offset matters
+    assert not torch.equal(O.dropout_keep_bits(99, 7, 0.5, n), O.dropout_keep_bits(100, 7, 0.5, n))  # and the seed
+    x = torch.arange(16, dtype=torch.float32) + 1
+    bits = torch.tensor([0b10100101, 0xff], dtype=torch.uint8)
+    out = O.dropout_apply(x, bits, 0.5)
+    assert out.tolist() == [2, 0, 6, 0, 0, 12, 0, 16, 18, 20, 22, 24, 26, 28, 30, 32]
