@@ -8,6 +8,10 @@
   c4_delayed  the same output in one pass with a caller-supplied scale (delayed scaling)
   c4_rowwise  the same output in one pass with one scale per row
   c4_mxfp8    the same in one pass as MXFP8 (one E8M0 scale byte per 32 elements)
+  c4_nvfp4    the same in one pass as NVFP4-style 4-bit output (e2m1, one e4m3 scale per 16
+              elements, caller-supplied tensor scale): 6.5625 bytes per element
+  c3_dropout  dropout -> residual-add -> LayerNorm forward, 16384 x 4096 bf16, with the keep
+              bits stored (8.125 bytes per element), and the dropout backward (4.125)
   dres        LayerNorm backward with incoming residual-stream gradient, 16384 x 8192 bf16
 
 CUDA events around back-to-back launches after warm-up; every tensor is larger than the
@@ -78,6 +82,13 @@ def c4(args, mode):
         fn = lambda: capi.norm_forward_fp8(capi.RMSNORM, x, r, g, None, q, s, None, rstd, amax, scale, 1e-6)
     elif mode == "delayed":
         fn = lambda: capi.norm_forward_fp8_delayed(capi.RMSNORM, x, r, g, None, q, s, None, None, scale, amax, 1e-6)
+    elif mode == "nvfp4":
+        q4 = torch.empty(rows, cols // 2, dtype=torch.uint8, device="cuda")
+        bs = torch.empty(rows, cols // 16, dtype=torch.uint8, device="cuda")
+        ts = torch.full((1,), 448.0 * 6.0 / 8.0, device="cuda")
+        fn = lambda: capi.norm_forward_nvfp4(capi.RMSNORM, x, r, g, None, q4, bs, s, None, None, ts, None, 1e-6)
+        t = loop_us(fn, args.warmup, args.iters)
+        return {"shape": [rows, cols], "us": t, "gbs_of_6.5625_bytes_per_element": 6.5625 * rows * cols / t / 1e3}
     elif mode == "mxfp8":
         bs = torch.empty(rows, cols // 32, dtype=torch.uint8, device="cuda")
         fn = lambda: capi.norm_forward_mxfp8(capi.RMSNORM, x, r, g, None, q, bs, s, None, None, None, 1e-6)
@@ -85,6 +96,22 @@ def c4(args, mode):
         fn = lambda: capi.norm_forward_fp8_rowwise(capi.RMSNORM, x, r, g, None, q, s, None, rstd, rs, None, 1e-6)
     t = loop_us(fn, args.warmup, args.iters)
     return {"shape": [rows, cols], "us": t, "gbs_of_7_bytes_per_element": 7 * rows * cols / t / 1e3}
+
+
+def c3_dropout(args):
+    rows, cols = 16384, 4096
+    x, r, ds = rnd(rows, cols), rnd(rows, cols, 0.5), rnd(rows, cols)
+    g = torch.ones(cols, device="cuda", dtype=BF)
+    b = torch.zeros(cols, device="cuda", dtype=BF)
+    y, s, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    bits = torch.empty(rows * cols // 8, dtype=torch.uint8, device="cuda")
+    tf = loop_us(lambda: capi.dropout_add_norm_forward(capi.LAYERNORM, x, r, g, b, y, s, mean, rstd, bits, 1e-5, 0.1, 1, 0),
+                 args.warmup, args.iters)
+    tb = loop_us(lambda: capi.dropout_backward(ds, bits, dx, 0.1, 1, 0), args.warmup, args.iters)
+    n = rows * cols
+    return {"shape": [rows, cols], "fwd_us": tf, "fwd_gbs": 8.125 * n / tf / 1e3, "dropout_bwd_us": tb,
+            "dropout_bwd_gbs": 4.125 * n / tb / 1e3}
 
 
 def dres(args):
@@ -103,7 +130,8 @@ def dres(args):
 CONFIGS = {
     "c3": lambda a: c3(a, False), "c3_dres": lambda a: c3(a, True),
     "c4": lambda a: c4(a, "two_phase"), "c4_delayed": lambda a: c4(a, "delayed"),
-    "c4_rowwise": lambda a: c4(a, "rowwise"), "c4_mxfp8": lambda a: c4(a, "mxfp8"), "dres": dres,
+    "c4_rowwise": lambda a: c4(a, "rowwise"), "c4_mxfp8": lambda a: c4(a, "mxfp8"),
+    "c4_nvfp4": lambda a: c4(a, "nvfp4"), "c3_dropout": c3_dropout, "dres": dres,
 }
 
 

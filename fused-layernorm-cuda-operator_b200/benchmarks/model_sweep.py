@@ -97,8 +97,9 @@ def one_config(model, hidden, batch, seq, dtype_name, warmup, iters):
         "pytorch_memory_mb": m_ref, "fused_memory_mb": m_fus,
         "memory_reduction": 1 - m_fus / m_ref if m_ref > 0 else 0.0,
         "max_diff": diff,
-        "fused_forward_gbs": 2 * rows * hidden * x.element_size() / (t_fus_f * 1e-3) / 1e9,
         "timestamp": datetime.now().isoformat(),
+        # added column, after the reference's
+        "fused_forward_gbs": 2 * rows * hidden * x.element_size() / (t_fus_f * 1e-3) / 1e9,
     }
 
 

@@ -27,6 +27,8 @@
 // registers as floats, statistics are the shifted two-pass form with sum reductions, 16-bit
 // values are widened / narrowed in pairs, fp8 codes are produced two at a time, and the FULL
 // instantiation carries no bounds checks.
+#include <cuda_fp4.h>
+
 #include "fln_common.cuh"
 
 namespace fln {
@@ -44,7 +46,7 @@ struct Fp8Params {
   float* scale;
   const float* scale_in;  // QMODE 1: one fp32, read by every CTA
   float* row_scale;       // QMODE 2: [rows] fp32, written
-  unsigned char* block_scale;  // QMODE 3: [rows, cols / 32] E8M0 bytes, written
+  unsigned char* block_scale;  // QMODE 3: [rows, cols / 32] E8M0 bytes; QMODE 4: [rows, cols / 16] e4m3 bytes; written
   int64_t rows;
   int cols;
   int nv;
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    if (QMODE != 3 && (FULL || (row_ok && iv < p.nv))) {
+    if (QMODE != 3 && QMODE != 4 && (FULL || (row_ok && iv < p.nv))) {
       float o[VEC];
       affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
 #pragma unroll
@@ -287,6 +289,46 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(cons
         pack_fp8<VEC>(o, out);
         st_stream<unsigned char, VEC>(qr + (int64_t)iv * VEC, out);
         if ((lane_r & (G - 1)) == 0) bs[iv / G] = (unsigned char)e8;
+      }
+    }
+  }
+  if (QMODE == 4) {
+    // NVFP4-style: e2m1 elements (two per byte, the even element in the low nibble), one e4m3
+    // scale per 16 consecutive elements of a row, one fp32 scale S for the tensor, supplied by
+    // the caller (typically 448 * 6 / amax of the previous step):
+    //   block scale  b = e4m3(block max * S / 6)     (round to nearest even, saturating)
+    //   element      q = e2m1(y * S / float(b))      (round to nearest even, saturating at 6)
+    // and y ~ e2m1(q) * float(b) / S.  The 16 elements of a block sit in G neighbouring lanes.
+    constexpr int G = 16 / VEC;
+    const float S = __ldg(p.scale_in);
+    unsigned char* __restrict__ bs = p.block_scale + (row_ok ? row : 0) * (int64_t)(p.cols / 16);
+    unsigned char* __restrict__ q4 = reinterpret_cast<unsigned char*>(p.q) + (base >> 1);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int iv = lane_r + k * tpr;
+      const bool act = FULL || (row_ok && iv < p.nv);
+      float o[VEC];
+      float bm = 0.f;
+      if (act) {
+        affine<TI, VEC>(o, f[k], rstd, gp, bp, (int64_t)iv * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) bm = fmaxf(bm, fabsf(o[i]));
+      }
+      amax = fmaxf(amax, bm);
+      // cols % 16 == 0, so the G lanes of a block are all active or all idle
+#pragma unroll
+      for (int off = 1; off < G; off <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, off));
+      const unsigned char sb = (unsigned char)__nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(bm, S), 1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+      const float fb = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
+      const float inv = fb > 0.f ? __fdiv_rn(S, fb) : 0.f;
+      if (act) {
+        Pack<unsigned char, VEC / 2> out;
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i)
+          out.e[i] = (unsigned char)__nv_cvt_float2_to_fp4x2(make_float2(__fmul_rn(o[2 * i], inv), __fmul_rn(o[2 * i + 1], inv)),
+                                                            __NV_E2M1, cudaRoundNearest);
+        st_stream<unsigned char, VEC / 2>(q4 + (int64_t)iv * (VEC / 2), out);
+        if ((lane_r & (G - 1)) == 0) bs[iv / G] = sb;
       }
     }
   }
@@ -364,12 +406,27 @@ static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
   constexpr int VFULL = 16 / sizeof(TI);
   Plan pl = make_plan(false, p.rows, p.cols, (int)sizeof(TI), true);
   if (pl.generic || pl.vec != VFULL) return FLN_ERR_UNSUPPORTED;
+  // block-scaled outputs: the vectors of one block must sit in neighbouring lanes, so a row needs
+  // at least as many threads as a block has vectors (very short rows: spread them out)
+  const int block_lanes = qmode == 3 ? 32 / VFULL : (qmode == 4 ? 16 / VFULL : 1);
+  if (pl.tpr < block_lanes && (qmode != 3 || p.cols % 32 == 0)) {
+    const int nvv = p.cols / VFULL;
+    int k = 1;
+    while (k * block_lanes < nvv) k <<= 1;
+    if (k <= 8) {
+      pl.tpr = block_lanes;
+      pl.log2_tpr = block_lanes == 1 ? 0 : (block_lanes == 2 ? 1 : (block_lanes == 4 ? 2 : 3));
+      pl.K = k;
+      pl.rows_per_cta = pl.threads / pl.tpr;
+    }
+  }
   p.tpr = pl.tpr;
   p.log2_tpr = pl.log2_tpr;
   p.nv = p.cols / VFULL;
   const unsigned grid = (unsigned)((p.rows + pl.rows_per_cta - 1) / pl.rows_per_cta);
   const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
   if (qmode == 3 && (p.cols % 32 != 0 || pl.tpr < 32 / VFULL)) return FLN_ERR_UNSUPPORTED;
+  if (qmode == 4 && (p.cols % 16 != 0 || pl.tpr < 16 / VFULL)) return FLN_ERR_UNSUPPORTED;
   if (p.amax != nullptr && cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
 #define FLN_FP8_LAUNCH(KK, FF)                                                                  \
   if (qmode == 0) {                                                                             \
@@ -379,6 +436,8 @@ static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 1><<<grid, pl.threads, 0, st>>>(p);               \
   } else if (qmode == 3) {                                                                      \
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 3><<<grid, pl.threads, 0, st>>>(p);               \
+  } else if (qmode == 4) {                                                                      \
+    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 4><<<grid, pl.threads, 0, st>>>(p);               \
   } else {                                                                                      \
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 2><<<grid, pl.threads, 0, st>>>(p);               \
   }
@@ -416,9 +475,9 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
   if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
   if (qmode == 0 && (amax == nullptr || scale == nullptr)) return FLN_ERR_NULL;
-  if (qmode == 1 && scale_in == nullptr) return FLN_ERR_NULL;
+  if ((qmode == 1 || qmode == 4) && scale_in == nullptr) return FLN_ERR_NULL;
   if (qmode == 2 && row_scale == nullptr) return FLN_ERR_NULL;
-  if (qmode == 3 && block_scale == nullptr) return FLN_ERR_NULL;
+  if ((qmode == 3 || qmode == 4) && block_scale == nullptr) return FLN_ERR_NULL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (rows == 0) {
     // empty tensor: amax = 0, scale = 1
@@ -501,4 +560,13 @@ extern "C" int fln_norm_forward_mxfp8(int kind, const void* x, const void* resid
                                       int io_dtype, float eps, void* stream) {
   return fp8_entry(3, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, nullptr, nullptr,
                    rows, cols, io_dtype, eps, stream, block_scale);
+}
+
+extern "C" int fln_norm_forward_nvfp4(int kind, const void* x, const void* residual, const void* gamma,
+                                      const void* beta, void* q, unsigned char* block_scale, void* sum_out,
+                                      float* mean, float* rstd, const float* tensor_scale_in, float* amax_out,
+                                      int64_t rows, int64_t cols, int io_dtype, float eps, void* stream) {
+  if (cols > 0 && cols % 16 != 0) return FLN_ERR_UNSUPPORTED;
+  return fp8_entry(4, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax_out, nullptr, tensor_scale_in,
+                   nullptr, rows, cols, io_dtype, eps, stream, block_scale);
 }

@@ -9,7 +9,7 @@ no CPU or pure-PyTorch fallback: importing this package needs the built extensio
 from .layernorm import (FusedLayerNorm, FusedLayerNormFunction, fused_layer_norm, replace_layernorm_modules,
                         replace_torch_layernorm, restore_torch_layernorm)
 from .rmsnorm import (FusedRMSNorm, fused_add_layer_norm, fused_add_layer_norm_fp8, fused_add_norm_fp8_delayed,
-                      fused_add_norm_fp8_rowwise, fused_add_norm_mxfp8, fused_add_rms_norm,
+                      fused_add_norm_fp8_rowwise, fused_add_norm_mxfp8, fused_add_norm_nvfp4, fused_add_rms_norm,
                       fused_add_rms_norm_fp8, fused_dropout_add_layer_norm, fused_rms_norm)
 
 __version__ = "1.0.0"
@@ -31,6 +31,7 @@ __all__ = [
     "fused_add_norm_fp8_delayed",
     "fused_add_norm_fp8_rowwise",
     "fused_add_norm_mxfp8",
+    "fused_add_norm_nvfp4",
     "fused_dropout_add_layer_norm",
 ]
 

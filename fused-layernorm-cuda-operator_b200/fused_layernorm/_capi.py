@@ -31,7 +31,7 @@ SYMBOLS = [
     "fln_set_path_override", "fln_device_status", "fln_layernorm_backward_static", "fln_set_sm_reserve",
     "fln_norm_forward_fp8_delayed", "fln_norm_forward_fp8_rowwise", "fln_norm_forward_mxfp8",
     "fln_planner_selftest", "fln_sum_rows_f32", "fln_set_stage_override", "fln_set_wait_limit_ns",
-    "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial", "fln_dropout_add_norm_forward", "fln_dropout_backward",
+    "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial", "fln_dropout_add_norm_forward", "fln_dropout_backward", "fln_norm_forward_nvfp4",
 ]
 STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
 
@@ -68,6 +68,7 @@ def lib() -> C.CDLL:
     L.fln_norm_forward_fp8_delayed.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_norm_forward_fp8_rowwise.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_norm_forward_mxfp8.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
+    L.fln_norm_forward_nvfp4.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, vp]
     L.fln_backward_workspace_bytes.restype = sz
     L.fln_backward_workspace_bytes.argtypes = [i64, i64, i32]
     L.fln_layernorm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, vp]
@@ -202,6 +203,16 @@ def dropout_backward(d_sum, keep_bits, d_x, p, seed, offset, stream=None):
     rows, cols = d_sum.shape
     check(lib().fln_dropout_backward(ptr(d_sum), ptr(keep_bits), ptr(d_x), rows, cols, dtype_code(d_sum), p, seed,
                                      offset, stream_handle(stream)), "fln_dropout_backward")
+
+
+def norm_forward_nvfp4(kind, x, residual, gamma, beta, q, block_scale, sum_out, mean, rstd, tensor_scale, amax_out, eps,
+                       stream=None):
+    """One launch: NVFP4-style output.  q: uint8 [rows, cols // 2] (two e2m1 per byte), block_scale:
+    uint8 [rows, cols // 16] (e4m3), tensor_scale: one fp32 on the device."""
+    rows, cols = x.shape
+    check(lib().fln_norm_forward_nvfp4(kind, ptr(x), ptr(residual), ptr(gamma), ptr(beta), ptr(q), ptr(block_scale),
+                                       ptr(sum_out), ptr(mean), ptr(rstd), ptr(tensor_scale), ptr(amax_out), rows, cols,
+                                       dtype_code(x), eps, stream_handle(stream)), "fln_norm_forward_nvfp4")
 
 
 def backward_workspace_bytes(rows, cols, dtype) -> int:

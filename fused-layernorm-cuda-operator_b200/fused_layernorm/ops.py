@@ -319,3 +319,33 @@ def _dan_backward(ctx, gy, gsum, _gmean, _grstd, _gbits):
 
 
 torch.library.register_autograd("fused_layernorm::dropout_add_norm_fwd", _dan_backward, setup_context=_dan_setup)
+
+
+@torch.library.custom_op("fused_layernorm::norm_nvfp4", mutates_args=())
+def norm_nvfp4(kind: int, input: torch.Tensor, residual: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
+               beta: Optional[torch.Tensor], tensor_scale: torch.Tensor,
+               epsilon: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(q, sum, block_scales, amax): NVFP4-style output of norm(input + residual) -- q uint8
+    [rows, cols / 2] (two e2m1 codes per byte), block_scales uint8 [rows, cols / 16] (e4m3),
+    amax fp32 [1] of this call; sum is empty without a residual.  Forward only."""
+    if input.dim() != 2 or not input.is_cuda:
+        raise RuntimeError("norm_nvfp4 expects a 2-D CUDA tensor")
+    x = input.contiguous()
+    res = residual.contiguous() if residual is not None else None
+    rows, cols = x.shape
+    q = x.new_empty((rows, cols // 2), dtype=torch.uint8)
+    bs = x.new_empty((rows, cols // 16), dtype=torch.uint8)
+    s = torch.empty_like(x) if res is not None else x.new_empty((0,))
+    amax = x.new_zeros((1,), dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        _capi.norm_forward_nvfp4(kind, x, res, gamma, beta, q, bs, s if res is not None else None, None, None,
+                                 tensor_scale, amax, epsilon)
+    return q, s, bs, amax
+
+
+@norm_nvfp4.register_fake
+def _(kind, input, residual, gamma, beta, tensor_scale, epsilon):
+    rows, cols = input.shape
+    s = torch.empty_like(input, memory_format=torch.contiguous_format) if residual is not None else input.new_empty((0,))
+    return (input.new_empty((rows, cols // 2), dtype=torch.uint8), s,
+            input.new_empty((rows, cols // 16), dtype=torch.uint8), input.new_empty((1,), dtype=torch.float32))

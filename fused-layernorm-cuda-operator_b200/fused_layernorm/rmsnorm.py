@@ -164,6 +164,21 @@ def fused_add_norm_mxfp8(input: torch.Tensor, residual: Optional[torch.Tensor] =
     return q.reshape(input.shape), (s.reshape(input.shape) if residual is not None else None), scales
 
 
+def fused_add_norm_nvfp4(input: torch.Tensor, tensor_scale: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                         weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                         rms: bool = True):
+    """(q, block_scales, amax, sum-or-None): one-pass NVFP4-style output of norm(input + residual):
+    e2m1 codes two per byte, one e4m3 scale per 16 elements, the fp32 tensor scale supplied by
+    the caller (448 * 6 / amax of the previous step); y ~ e2m1(q) * e4m3(block_scale) / tensor_scale.
+    The last dimension must be a multiple of 16.  Forward only."""
+    _require_cuda(input)
+    kind = _ops.RMSNORM if rms else _ops.LAYERNORM
+    res = _flat(residual) if residual is not None else None
+    q, s, bs, amax = _t.norm_nvfp4(kind, _flat(input), res, weight, None if rms else bias, tensor_scale, float(eps))
+    lead = input.shape[:-1]
+    return (q.reshape(*lead, -1), bs.reshape(*lead, -1), amax, s.reshape(input.shape) if residual is not None else None)
+
+
 class FusedRMSNorm(nn.Module):
     """torch.nn.RMSNorm-compatible module (normalized_shape, eps, elementwise_affine; parameter `weight`)."""
 

@@ -238,6 +238,23 @@ int fln_cast_from_f32(const float* src, void* dst, int64_t n, int dtype, void* s
 int fln_sum_rows_f32(const float* rows_in, int64_t n_rows, int64_t ncols, float* out_f32,
                      void* out_cast, int dtype, void* stream);
 
+/* One-pass forward with NVFP4-style block-scaled 4-bit output (the second block-scaled input
+ * format of Blackwell's tensor cores): e2m1 elements, one e4m3 scale per 16 consecutive
+ * elements of a row, one fp32 scale S for the whole tensor, supplied by the caller (delayed
+ * scaling: typically 448 * 6 / amax of the previous step; amax_out reports this call's max|y|).
+ *   block_scale[r, c / 16] = e4m3(max|y| of the block * S / 6)      round to nearest even, saturating
+ *   q element              = e2m1(y * S / float(block_scale))        round to nearest even, saturating at 6
+ *   y ~ e2m1(q) * float(block_scale) / S
+ *   q            [rows, cols / 2] bytes: element 2 i in the low nibble, 2 i + 1 in the high one
+ *   block_scale  [rows, cols / 16] bytes (e4m3), required
+ *   tensor_scale_in  one fp32 on the device, required
+ * cols must be a multiple of 16; other rules as fln_norm_forward_fp8.  No counterpart in the
+ * reference. */
+int fln_norm_forward_nvfp4(int kind, const void* x, const void* residual, const void* gamma,
+                           const void* beta, void* q, unsigned char* block_scale, void* sum_out,
+                           float* mean, float* rstd, const float* tensor_scale_in, float* amax_out,
+                           int64_t rows, int64_t cols, int io_dtype, float eps, void* stream);
+
 /* Fused dropout -> residual add -> LayerNorm / RMSNorm forward: the step in front of the
  * normalization in a pre-norm block, in one pass.
  *   d = dropout(x, p): kept elements times 1 / (1 - p'), rounded to the I/O type

@@ -381,3 +381,65 @@ API void oracle_dropout_apply(const void* x, const uint8_t* bits, void* out, int
     store_el(out, i, dt, keep ? (float)load_el(x, i, dt) * scale : 0.0f);
   }
 }
+
+/* ------------------------------------------------------------------ NVFP4-style quantizer */
+
+/* e4m3 code -> value (finite codes) */
+static float e4m3_to_f(uint8_t c) {
+  const int sign = c >> 7, e = (c >> 3) & 15, m = c & 7;
+  const float v = e == 0 ? ldexpf((float)m, -9) : ldexpf((float)(8 + m), e - 10);
+  return sign ? -v : v;
+}
+/* e2m1: magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6 (codes 0..7), sign in bit 3; round to nearest,
+ * ties to the even code, saturating at 6; NaN gives +6 like the hardware conversion. */
+static uint8_t f_to_e2m1_sat(float v) {
+  static const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  if (v != v) return 7;
+  const uint8_t sign = signbit(v) ? 8 : 0;
+  const float a = fabsf(v);
+  int code = 7;
+  for (int c = 0; c < 7; ++c) {
+    const float mid = 0.5f * (mag[c] + mag[c + 1]);
+    if (a < mid || (a == mid && (c & 1) == 0)) { code = c; break; }
+  }
+  return (uint8_t)(sign | code);
+}
+API float oracle_e2m1_decode(uint8_t c) {
+  static const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  return (c & 8) ? -mag[c & 7] : mag[c & 7];
+}
+API float oracle_e4m3_decode(uint8_t c) { return e4m3_to_f(c); }
+
+/*
+ * y32 [rows, cols] -> q [rows, cols / 2] (element 2 i in the low nibble), block_scale
+ * [rows, cols / 16] e4m3.  tensor scale S (fp32):  b = e4m3(block max * S / 6),
+ * q = e2m1(y * (S / float(b))), all in fp32 with one rounding per operation, as
+ * fln_norm_forward_nvfp4 states it.  With scales_in != NULL those block scales are used
+ * instead of being derived (and copied to block_scale).
+ */
+API void oracle_quant_nvfp4(const float* y32, int64_t rows, int64_t cols, float S, const uint8_t* scales_in,
+                            uint8_t* q, uint8_t* block_scale) {
+  const int64_t nb = cols / 16;
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t b = 0; b < nb; ++b) {
+      const float* y = y32 + r * cols + b * 16;
+      float bm = 0.f;
+      for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(y[i]));
+      uint8_t sb;
+      if (scales_in) {
+        sb = scales_in[r * nb + b];
+      } else {
+        volatile float t = bm * S;
+        volatile float d = t * (1.0f / 6.0f);
+        sb = f_to_e4m3_sat(d);
+      }
+      block_scale[r * nb + b] = sb;
+      const float fb = e4m3_to_f(sb);
+      const float inv = fb > 0.f ? S / fb : 0.f;
+      for (int i = 0; i < 16; i += 2) {
+        volatile float a0 = y[i] * inv, a1 = y[i + 1] * inv;
+        q[(r * cols + b * 16 + i) / 2] = (uint8_t)(f_to_e2m1_sat(a0) | (f_to_e2m1_sat(a1) << 4));
+      }
+    }
+  }
+}

@@ -55,6 +55,11 @@ def lib() -> C.CDLL:
         L.oracle_convert_from_f32.argtypes = [f32p, vp, i64, i32]
         L.oracle_convert_to_f32.argtypes = [vp, f32p, i64, i32]
         L.oracle_e4m3_encode.argtypes = [f32p, vp, i64]
+        L.oracle_quant_nvfp4.argtypes = [f32p, i64, i64, C.c_float, vp, vp, vp]
+        L.oracle_e2m1_decode.argtypes = [C.c_uint8]
+        L.oracle_e2m1_decode.restype = C.c_float
+        L.oracle_e4m3_decode.argtypes = [C.c_uint8]
+        L.oracle_e4m3_decode.restype = C.c_float
         L.oracle_philox4x32_10.argtypes = [vp, vp, vp]
         L.oracle_dropout_keep_bits.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, i64, vp]
         L.oracle_dropout_apply.argtypes = [vp, vp, vp, i64, i32, C.c_float]
@@ -296,3 +301,29 @@ def dropout_apply(x, bits, p: float):
     _, scale = dropout_threshold(p)
     lib().oracle_dropout_apply(_ptr(x), _ptr(bits), _ptr(out), x.numel(), DT[x.dtype], scale)
     return out
+
+
+E2M1_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+
+
+def quant_nvfp4(y32, tensor_scale: float, block_scales=None):
+    """NVFP4-style quantization of y32 [rows, cols]: (q uint8 [rows, cols // 2] with element 2 i in
+    the low nibble, block scales uint8 [rows, cols // 16] in e4m3).  With block_scales given,
+    those are used instead of being derived."""
+    y32 = _c(y32).float()
+    rows, cols = y32.shape
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8)
+    bs = torch.empty(rows, cols // 16, dtype=torch.uint8)
+    lib().oracle_quant_nvfp4(_ptr(y32), rows, cols, float(tensor_scale), _ptr(_c(block_scales)), _ptr(q), _ptr(bs))
+    return q, bs
+
+
+def dequant_nvfp4(q, block_scales, tensor_scale: float):
+    """fp32 [rows, cols] from the packed e2m1 codes, the e4m3 block scales and the tensor scale."""
+    rows, half = q.shape
+    lut = torch.tensor(E2M1_VALUES + [-v for v in E2M1_VALUES], dtype=torch.float32)
+    lo, hi = lut[(q & 15).long()], lut[(q >> 4).long()]
+    vals = torch.stack([lo, hi], dim=-1).reshape(rows, half * 2)
+    e4 = torch.tensor([lib().oracle_e4m3_decode(c) for c in range(256)], dtype=torch.float32)
+    f = e4[block_scales.long()].repeat_interleave(16, dim=1)
+    return vals * f / tensor_scale
