@@ -208,8 +208,45 @@ bool pipeline_wanted(const PipePlan& P, int64_t rows) {
   return n_tiles >= 4LL * P.grid || n_tiles >= 8LL * sm_count();
 }
 
+// clusters of two backward CTAs that are resident at once on the current device: half the SMs
+// until the backward's launcher has asked the runtime (cudaOccupancyMaxActiveClusters)
+static std::atomic<int> g_pair_slots[64];
+int pair_slots() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    dev = 0;
+  }
+  const int v = g_pair_slots[dev].load(std::memory_order_relaxed);
+  const int half = usable_sms() / 2;
+  return v > 0 && v < half ? v : (half > 0 ? half : 1);
+}
+void set_pair_slots(int n) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return;
+  }
+  g_pair_slots[dev].store(n, std::memory_order_relaxed);
+}
+
+// Rows beyond the register budget of one CTA (16-bit rows above 12288 columns, fp32 rows above
+// 8192) are shared by the two CTAs of a
+// thread-block cluster: each CTA stages and differentiates half of every row, the two row sums
+// cross through distributed shared memory.  The plan is the half row's plan (512 threads per
+// half row, one row per tile) with `pair` set and the grid counted in CTAs (two per row slot).
 PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
-  return plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
+  PipePlan P = plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
+  if (!P.ok && !with_dres && cols % 2 == 0 && g_path_override.load(std::memory_order_relaxed) != 3) {
+    PipePlan H = plan_pipeline(true, rows, cols / 2, es, 2);
+    if (H.ok && H.full && H.threads == 512 && H.g.tpr == 512 && H.g.R == 1 && H.K * (H.vb / es) <= 20) {
+      H.pair = true;
+      const int64_t slots = pair_slots();
+      H.grid = (int)(2 * (rows < slots ? rows : slots));
+      return H;
+    }
+  }
+  return P;
 }
 
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
@@ -237,7 +274,7 @@ int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, b
   const int es = dtype == FLN_F32 ? 4 : 2;
   PipePlan P = plan_bwd_pipeline(rows, cols, es, with_dres);
   if (!pipeline_wanted(P, rows)) return 0;
-  return (int64_t)P.grid * P.g.R;
+  return P.pair ? (int64_t)(P.grid / 2) : (int64_t)P.grid * P.g.R;
 }
 
 

@@ -114,6 +114,35 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// ----------------------------------------------------------------------------------------
+// Thread-block cluster helpers (a row shared by the two CTAs of a cluster, backward only):
+// distributed shared memory by plain st.shared::cluster -- no multicast of any kind -- and the
+// hardware cluster barrier.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  cluster_arrive();
+  cluster_wait();
+}
+// address of `p` (a shared-memory address of this CTA) in the shared memory of CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 // One 16-byte vector of a stage as ONE 128-bit shared-memory load.  (Handing the stage to the
 // conversion helper by reference lets the compiler read it word by word: four times the load
 // instructions and the shared-memory pipe becomes the stall.)
@@ -213,6 +242,7 @@ __device__ __forceinline__ void grid_depart(unsigned long long* w, unsigned int 
 struct PipePlan {
   bool ok;
   bool full;  // branch-free instantiation applies
+  bool pair;  // backward only: a row is shared by the two CTAs of a cluster (each half a row)
   int vb;     // bytes per vector: 16, or 8 / 4 where that makes the row divide evenly
   int K;
   int threads;
@@ -244,6 +274,8 @@ struct DeviceWords {
 constexpr int kSchedSlots = 1024;
 bool device_words(DeviceWords* out);  // of the current device; false if they cannot be had
 unsigned int next_sched_slot();       // every pipelined forward launch takes the next pair
+int pair_slots();                     // clusters of two 512-thread CTAs resident at once (set by the backward)
+void set_pair_slots(int n);
 
 template <typename F>
 static int set_smem(F kernel, size_t smem) {

@@ -108,7 +108,16 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb, 
 // LT >= 0: geometry known at compile time (a CTA of 512 threads, 2^LT threads per row, rows of
 // exactly K * VEC * 2^LT elements), as in the forward: 15.1 instead of 19.9 instructions per
 // element for bf16 at 16384 x 8192.
-template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES, int VB = 16, int LT = -1>
+// PAIR: launched as clusters of two CTAs that share every row: CTA `rank` of the cluster stages
+// and differentiates columns [rank * cols, rank * cols + cols) of a row of 2 * cols (cols = the
+// half row, K * VEC * 512: one row per tile, 512 threads per half row).  The two partial row
+// sums of each CTA's 16 warps go into the partner's shared memory as well (st.shared::cluster);
+// the hardware cluster barrier takes the place of the CTA barrier of every row (it releases
+// the stage and publishes the sums), and both CTAs add the 32 values of a sum in the same
+// order.  The cluster barrier has no bounded form, so no CTA may skip one: a CTA whose wait for
+// a copy ran out flags it, stops working and keeps meeting its partner at the barrier for the
+// rows that remain (both CTAs of a cluster have the same number of rows).
+template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES, int VB = 16, int LT = -1, bool PAIR = false>
 __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(T);  // even
   constexpr int V2 = VEC / 2;
@@ -117,6 +126,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   static_assert(!CT || FULL, "compile-time geometry is for the FULL kernel");
+  static_assert(!PAIR || (LT == 9 && !FUSE && !DRES), "a shared row: 512 threads per half row, plain stage 1");
   const int tpr = CT ? (1 << LTC) : g.tpr;
   const int log2_tpr = CT ? LTC : g.log2_tpr;
   const int R = CT ? (512 >> LTC) : g.R;
@@ -126,34 +136,51 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   const uint32_t stage_stride = CT ? second_off * (uint32_t)NPROD : g.stage_stride;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 floats
+  int* pair_flag = reinterpret_cast<int*>(smem + 192);  // PAIR: set by a thread whose wait for a copy ran out
+  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 floats (PAIR: 2 x [2 ranks][64])
   unsigned char* stages = smem + kSmemHeader;
 
   const int tid = threadIdx.x;
   const int lane_r = tid & (tpr - 1);
   const int r_in = tid >> log2_tpr;
   const int S = g.S;
-  const int my_tiles = my_tile_count((p.rows + R - 1) / R);
-  const float inv_n = 1.0f / (float)cols;
+  // row slots of the static split: CTAs, or clusters when two CTAs share a row
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  // Measured, not derived: the 16-bit kernels are a third slower (16384 x 8192 bf16: 177 against
+  // 133 us) when the slot and the slot count live in registers across the row loop instead of
+  // being read from the special registers at each use, and the fp32 kernels are a tenth faster
+  // (16384 x 8192: 239 against 266 us).  Register counts are the same within three either way.
+  constexpr bool HOLD = sizeof(T) == 4;
+  const int slot_r = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int nslot_r = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+#define FLN_SLOT (HOLD ? (int64_t)slot_r : (int64_t)(PAIR ? (blockIdx.x >> 1) : blockIdx.x))
+#define FLN_NSLOT (HOLD ? (int64_t)nslot_r : (int64_t)(PAIR ? (gridDim.x >> 1) : gridDim.x))
+  const int ld = PAIR ? 2 * cols : cols;            // elements from one row to the next
+  const int coff = PAIR ? (int)rank * cols : 0;     // first column of this CTA
+  const int64_t n_tiles = (p.rows + R - 1) / R;
+  const int my_tiles = (int64_t)FLN_SLOT < n_tiles ? (int)((n_tiles - FLN_SLOT + FLN_NSLOT - 1) / FLN_NSLOT) : 0;
+  const float inv_n = 1.0f / (float)ld;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], NPROD);
+    if (PAIR) *reinterpret_cast<volatile int*>(pair_flag) = 0;
     mbar_init_fence();
   }
   if (FUSE && tid == 96) grid_barrier_init(p.sync, p.token);
-  __syncthreads();
+  if (PAIR) cluster_sync_all();  // the partner's barriers exist before anything remote happens
+  else __syncthreads();
 
   // producer `which` (0: dy, 1: x, 2: dres_in) arms stage s with its share of tile i
   const int which = tid >> 5;
   const bool is_producer = (tid & 31) == 0 && which < NPROD;
   auto issue = [&](int i, int s, bool skip_copy) {
-    const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)i * gridDim.x) * R;
+    const int64_t row0 = ((int64_t)FLN_SLOT + (int64_t)i * FLN_NSLOT) * R;
     const int64_t left = p.rows - row0;
     const uint32_t bytes = (uint32_t)(left < R ? left : R) * row_bytes;
     unsigned char* dst = stages + (size_t)s * stage_stride + (size_t)which * second_off;
     const T* src = reinterpret_cast<const T*>(which == 0 ? p.dy : (which == 1 ? p.x : p.dres_in));
     mbar_expect_tx(&full[s], bytes);
-    if (!skip_copy) bulk_g2s(dst, src + row0 * cols, bytes, &full[s]);
+    if (!skip_copy) bulk_g2s(dst, src + row0 * ld + coff, bytes, &full[s]);
   };
   if (is_producer) {
     // test hook (fln_set_test_fault bit 0): CTA 0 arms its first stage without the dy copy
@@ -175,12 +202,12 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
       gam[k][e] = f2(1.f);
     }
     if (p.gamma != nullptr && vok[k])
-      unpack2<T, VEC>(ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
+      unpack2<T, VEC>(ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + coff + (int64_t)iv * VEC), gam[k]);
   }
 
   // per-row statistics of the next tile are fetched one iteration ahead
-  int64_t row = (int64_t)blockIdx.x * R + r_in;
-  const int64_t row_step = (int64_t)gridDim.x * R;
+  int64_t row = (int64_t)FLN_SLOT * R + r_in;
+  const int64_t row_step = (int64_t)FLN_NSLOT * R;
   float mean_n = 0.f, rstd_n = 0.f;
   if (my_tiles > 0 && row < p.rows) {
     if (KIND == FLN_LAYERNORM) mean_n = __ldg(p.mean + row);
@@ -242,14 +269,42 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     float red[NR];
     red[0] = r0.x + r0.y;
     if (KIND == FLN_LAYERNORM) red[NR - 1] = r1.x + r1.y;
-    float* sr = s_red + (i & 1) * 64;
-    rowsum_warp<NR>(red, tpr, sr);
-    if (!__syncthreads_and(landed ? 1 : 0)) {
-      aborted = true;
-      break;
+    float* sr = s_red + (i & 1) * (PAIR ? 128 : 64);
+    if constexpr (PAIR) {
+      // the warp's sums into this CTA's half of the table and into the partner's copy of it
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int n = 0; n < NR; ++n) red[n] += __shfl_xor_sync(0xffffffffu, red[n], off);
+      }
+      if ((tid & 31) == 0) {
+        float* mine = sr + rank * 64 + (tid >> 5);
+        const uint32_t theirs = map_to_cta(mine, rank ^ 1u);
+#pragma unroll
+        for (int n = 0; n < NR; ++n) {
+          mine[n * 32] = red[n];
+          st_cluster_f32(theirs + n * 32 * 4, red[n]);
+        }
+      }
+      if (!landed) *reinterpret_cast<volatile int*>(pair_flag) = 1;
+      cluster_arrive();
+      cluster_wait();
+      if (*reinterpret_cast<volatile int*>(pair_flag) != 0) {
+        aborted = true;
+        break;
+      }
+      if (is_producer && i + S < my_tiles) issue(i + S, s, false);
+#pragma unroll
+      for (int n = 0; n < NR; ++n) red[n] = sum_w<16>(sr + n * 32) + sum_w<16>(sr + 64 + n * 32);
+    } else {
+      rowsum_warp<NR>(red, tpr, sr);
+      if (!__syncthreads_and(landed ? 1 : 0)) {
+        aborted = true;
+        break;
+      }
+      if (is_producer && i + S < my_tiles) issue(i + S, s, false);
+      rowsum_cta<NR>(red, tpr, sr);
     }
-    if (is_producer && i + S < my_tiles) issue(i + S, s, false);
-    rowsum_cta<NR>(red, tpr, sr);
     // dx = rstd * ((g - c2) - xhat * c1): the subtraction comes first so that rows whose g
     // is (nearly) constant cancel exactly instead of leaving a rounding residue times rstd
     const float2 nc1 = f2(-(red[0] * inv_n));
@@ -257,7 +312,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     const float2 nc2 = f2(-c2s);
 
     if (p.dx != nullptr) {
-      T* __restrict__ dxr = reinterpret_cast<T*>(p.dx) + row * (int64_t)cols + (int64_t)lane_r * VEC;
+      T* __restrict__ dxr = reinterpret_cast<T*>(p.dx) + row * (int64_t)ld + coff + (int64_t)lane_r * VEC;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         if (FULL || (row_ok && vok[k])) {
@@ -296,10 +351,14 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     }
   }
   if (aborted && tid == 0) pipeline_abort(p.status, full, S, s, phase, my_tiles - i < S ? my_tiles - i : S, p.wait_ns);
+  if (PAIR && aborted) {
+    // keep the partner company at the barriers of the rows this CTA no longer works on
+    for (int j = i + 1; j < my_tiles; ++j) cluster_sync_all();
+  }
 
   if (p.partials != nullptr && !aborted) {
-    const int64_t prow = (int64_t)blockIdx.x * R + r_in;
-    float* __restrict__ pg = p.partials + prow * (int64_t)(NR * cols);
+    const int64_t prow = (int64_t)FLN_SLOT * R + r_in;
+    float* __restrict__ pg = p.partials + prow * (int64_t)(NR * ld) + coff;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int iv = lane_r + k * tpr;
@@ -310,19 +369,22 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
             *reinterpret_cast<float4*>(pg + (int64_t)iv * VEC + 2 * e) =
                 make_float4(acc_g[k][e].x, acc_g[k][e].y, acc_g[k][e + 1].x, acc_g[k][e + 1].y);
             if (KIND == FLN_LAYERNORM)
-              *reinterpret_cast<float4*>(pg + cols + (int64_t)iv * VEC + 2 * e) =
+              *reinterpret_cast<float4*>(pg + ld + (int64_t)iv * VEC + 2 * e) =
                   make_float4(acc_b[k][e].x, acc_b[k][e].y, acc_b[k][e + 1].x, acc_b[k][e + 1].y);
           }
         } else {
 #pragma unroll
           for (int e = 0; e < V2; ++e) {
             *reinterpret_cast<float2*>(pg + (int64_t)iv * VEC + 2 * e) = acc_g[k][e];
-            if (KIND == FLN_LAYERNORM) *reinterpret_cast<float2*>(pg + cols + (int64_t)iv * VEC + 2 * e) = acc_b[k][e];
+            if (KIND == FLN_LAYERNORM) *reinterpret_cast<float2*>(pg + ld + (int64_t)iv * VEC + 2 * e) = acc_b[k][e];
           }
         }
       }
     }
   }
+
+  // neither CTA of a cluster leaves while the other might still write into its shared memory
+  if (PAIR) cluster_sync_all();
 
   if (FUSE) {
     ReduceArgs a;
@@ -341,9 +403,45 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   }
 }
 
+#undef FLN_SLOT
+#undef FLN_NSLOT
+
 template <typename KernelT>
 static int launch_bwd_kernel(KernelT kern, const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
+  if (P.pair) {
+    // clusters of two CTAs; the grid never exceeds what is resident at once
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)P.grid);
+    cfg.blockDim = dim3((unsigned)P.threads);
+    cfg.dynamicSmemBytes = P.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    static std::atomic<int> asked[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && asked[dev].load(std::memory_order_relaxed) == 0) {
+      int n = 0;
+      cudaLaunchConfig_t probe = cfg;
+      probe.gridDim = dim3(2u * (unsigned)(usable_sms() / 2 > 0 ? usable_sms() / 2 : 1));
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &probe) == cudaSuccess && n > 0) set_pair_slots(n);
+      else cudaGetLastError();
+      asked[dev].store(1, std::memory_order_relaxed);
+      if (n > 0 && 2 * n < P.grid) return FLN_PIPE_NOT_APPLICABLE;  // planned for more clusters than fit: plan again
+    }
+    if (cudaLaunchKernelEx(&cfg, kern, p, P.g) != cudaSuccess) {
+      cudaGetLastError();
+      return FLN_ERR_LAUNCH;
+    }
+    FLN_CHECK_LAUNCH();
+    return FLN_OK;
+  }
   if (p.sync != nullptr) {
     // the grid barrier needs every CTA resident: cooperative launch
     cudaLaunchConfig_t cfg;
@@ -374,6 +472,15 @@ static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) 
   constexpr int VEC = VB / (int)sizeof(T);
   if constexpr (VEC >= 2 && KK * VEC <= (sizeof(T) == 2 ? 24 : 16)) {
     const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
+    // geometry as template arguments for rows of 256 or 512 threads (no residual-stream gradient)
+    if (!dr && P.threads == 512 && (P.g.tpr == 512 || P.g.tpr == 256)) {
+      if (P.g.tpr == 512) {
+        if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, 9>, p, P, st);
+        return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, 9>, p, P, st);
+      }
+      if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, 8>, p, P, st);
+      return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, 8>, p, P, st);
+    }
     if (fuse && dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB>, p, P, st);
     if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB>, p, P, st);
     if (dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, true, VB>, p, P, st);
@@ -393,9 +500,25 @@ static int bwd_pipe_pow2(const BwdParams& p, const PipePlan& P, cudaStream_t st)
   return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, FF, false, false, 16, LT>, p, P, st);
 }
 
+// a row shared by the two CTAs of a cluster: the half row's plan decides the instantiation
+template <typename T, int KIND>
+static int bwd_pipe_pair(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+#define FLN_PAIR(KK, VBB)                                                                                       \
+  if (P.K == KK && P.vb == VBB) {                                                                               \
+    if constexpr ((VBB / (int)sizeof(T)) >= 2 && KK * (VBB / (int)sizeof(T)) <= 20)                             \
+      return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VBB, 9, true>, p, P, st);  \
+  }
+  FLN_PAIR(16 / VEC, 16) FLN_PAIR(3, 8) FLN_PAIR(5, 8) FLN_PAIR(7, 8) FLN_PAIR(3, 16) FLN_PAIR(5, 4)
+  FLN_PAIR(7, 4) FLN_PAIR(3, 4)
+#undef FLN_PAIR
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
 template <typename T, int KIND>
 static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
+  if (P.pair) return bwd_pipe_pair<T, KIND>(p, P, st);
   if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) {
     if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_ODD(KK, VBB) \
@@ -412,6 +535,8 @@ static int bwd_pipe_k(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
       if constexpr (VEC * KK == 16) {                                                                  \
         if (P.full && P.threads == 512 && P.g.tpr == 512) return bwd_pipe_pow2<T, KIND, KK, true, 9>(p, P, st); \
         if (P.full && P.threads == 512 && P.g.tpr == 256) return bwd_pipe_pow2<T, KIND, KK, true, 8>(p, P, st); \
+        if (P.full && P.threads == 512 && P.g.tpr == 128) return bwd_pipe_pow2<T, KIND, KK, true, 7>(p, P, st); \
+        if (P.full && P.threads == 512 && P.g.tpr == 64) return bwd_pipe_pow2<T, KIND, KK, true, 6>(p, P, st);  \
       }                                                                                                \
       if (P.full) return bwd_pipe_pow2<T, KIND, KK, true, -1>(p, P, st);                               \
       return bwd_pipe_pow2<T, KIND, KK, false, -1>(p, P, st);                                          \
@@ -463,7 +588,7 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
   p.fault = w.fault;
   // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the
   // one-row kernel, stage memory large enough for the 16 x 128 floats of the combine step.
-  const bool fuse = p.sync != nullptr && p.partials != nullptr && P.grid <= usable_sms() &&
+  const bool fuse = !P.pair && p.sync != nullptr && p.partials != nullptr && P.grid <= usable_sms() &&
                     P.grid < 4096 && P.smem >= (size_t)kSmemHeader + 16 * 128 * sizeof(float) &&
                     path_override() != 3 && cooperative_launch_supported();
   if (fuse) {

@@ -24,7 +24,7 @@ namespace fln {
 // registers as floats, for plans that give a thread more than 32 elements (row lengths
 // 5 * 2^a in 16-bit types: 40 elements per thread keep the 16-byte vectors and move more
 // bytes per barrier than 20 elements in 8-byte vectors)
-// LT >= 0: the geometry is known at compile time -- a CTA of 256 threads, 2^LT threads per row,
+// LT >= 0: the geometry is known at compile time -- a CTA of 256 threads (512 for LT = 9), 2^LT threads per row,
 // rows of exactly K * VEC * 2^LT elements (FULL).  Row length, byte offsets of a thread's
 // vectors and the shape of the reductions then fold into immediates: the bf16 forward at
 // 16384 x 8192 executes 8.4 instead of 11.3 instructions per element and takes 83 instead of
@@ -37,10 +37,11 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   constexpr bool PSM = MODE == 4;
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
-  static_assert(!CT || MODE == 1, "compile-time geometry is for the plain FULL kernel");
+  constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
+  static_assert(!CT || MODE == 1 || MODE == 4, "compile-time geometry is for the FULL kernels");
   const int tpr = CT ? (1 << LTC) : g.tpr;
   const int log2_tpr = CT ? LTC : g.log2_tpr;
-  const int R = CT ? (256 >> LTC) : g.R;
+  const int R = CT ? (NT >> LTC) : g.R;
   const int cols = CT ? ((K * VEC) << LTC) : p.cols;
   const uint32_t row_bytes = CT ? (uint32_t)((K * VB) << LTC) : g.row_bytes;
   const uint32_t second_off = CT ? row_bytes * (uint32_t)R : g.second_off;
@@ -306,18 +307,29 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 template <typename TI, typename TO, int KIND, int ACT, int KK, int VB>
 static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = VB / (int)sizeof(TI);
-  if constexpr (VEC >= 4 && KK * VEC == 40 && sizeof(TI) == 2) {
-    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 4, VB>;
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
-    FLN_CHECK_LAUNCH();
-    return FLN_OK;
-  } else if constexpr (VEC >= 4 && KK * VEC <= 32) {
-    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 1, VB>;
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
-    FLN_CHECK_LAUNCH();
-    return FLN_OK;
+  constexpr int MODE = (VEC >= 4 && KK * VEC == 40 && sizeof(TI) == 2) ? 4 : ((VEC >= 4 && KK * VEC <= 32) ? 1 : -1);
+  if constexpr (MODE > 0) {
+#define FLN_GO(LTT)                                                             \
+  {                                                                             \
+    auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, MODE, VB, LTT>;     \
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                \
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                            \
+    FLN_CHECK_LAUNCH();                                                         \
+    return FLN_OK;                                                              \
+  }
+    // geometry as template arguments for the plain forward (no GELU, same type out as in)
+    if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
+      const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
+      if (P.threads == nt) {
+        if (P.g.tpr == 32) FLN_GO(5)
+        if (P.g.tpr == 64) FLN_GO(6)
+        if (P.g.tpr == 128) FLN_GO(7)
+        if (P.g.tpr == 256) FLN_GO(8)
+        if (P.g.tpr == 512) FLN_GO(9)
+      }
+    }
+    FLN_GO(-1)
+#undef FLN_GO
   } else {
     return FLN_PIPE_NOT_APPLICABLE;
   }
@@ -352,6 +364,9 @@ static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
     if constexpr (KK == 4) {                                        \
       if (P.full && P.threads == 256 && P.g.tpr == 256) FLN_LAUNCH_CT(KK, 8)      \
       else if (P.full && P.threads == 256 && P.g.tpr == 128) FLN_LAUNCH_CT(KK, 7) \
+      else if (P.full && P.threads == 256 && P.g.tpr == 64) FLN_LAUNCH_CT(KK, 6)  \
+      else if (P.full && P.threads == 256 && P.g.tpr == 32) FLN_LAUNCH_CT(KK, 5)  \
+      else if (P.full && P.threads == 512 && P.g.tpr == 512) FLN_LAUNCH_CT(KK, 9) \
       else if (P.full) FLN_LAUNCH(KK, 1)                            \
       else FLN_LAUNCH(KK, 0)                                        \
     } else if constexpr (KK * 16 / sizeof(TI) <= 32) {              \

@@ -508,7 +508,7 @@ def path_override():
     capi.lib().fln_set_path_override(0)
 
 
-@pytest.mark.parametrize("mode", [1, 2, 4])  # 1 = register kernels, 2 = bulk-async pipeline, 4 = + two-row backward
+@pytest.mark.parametrize("mode", [1, 2, 3])  # 1 = register kernels, 2 = bulk-async pipeline, 3 = 2 with dgamma / dbeta summed by a second launch
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype", [F32, BF16, F16])
 @pytest.mark.parametrize("shape", [(701, 4096), (333, 8192), (1500, 768), (2049, 1024), (97, 16384), (4099, 256)])
@@ -542,7 +542,14 @@ def test_kernel_families_agree_with_oracle(path_override, shape, dtype, kind, mo
         torch.testing.assert_close(gr["dx"], wr["dx32"], rtol=1e-5, atol=1e-5)
     else:
         U.assert_out_close(gr["dx"], wr["dx"], dtype)
-    assert torch.equal(gr["dgb_f32"], gb["dgb_f32"])
+    if cols <= (8192 if dtype == F32 else 12288):
+        assert torch.equal(gr["dgb_f32"], gb["dgb_f32"])
+    else:
+        # longer rows: without the residual-stream gradient a row may be shared by the two CTAs
+        # of a cluster, with it the long-row kernels run; the rows are then summed in another order
+        U.assert_param_grads_close(gr["dgb_f32"][:cols], wr["dgamma64"], wr["abs64"][0], rows)
+        if kind == "layernorm":
+            U.assert_param_grads_close(gr["dgb_f32"][cols:], wr["dbeta64"], wr["abs64"][1], rows)
     assert capi.lib().fln_device_status() == 0
 
 
@@ -567,6 +574,38 @@ def test_long_rows_backward(shape, dtype, kind):
             U.assert_param_grads_close(got["dgb_f32"][cols:], want["dbeta64"], want["abs64"][1], rows)
     only_params = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, want=(False, True, True))
     U.assert_param_grads_close(only_params["dgb_f32"][:cols], want["dgamma64"], want["abs64"][0], rows)
+
+
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype,shape", [(BF16, (1200, 16384)), (BF16, (700, 14336)), (F32, (900, 10240)),
+                                         (F32, (640, 16384)), (F16, (800, 20480)), (F32, (600, 12288)),
+                                         (F32, (500, 14336))])
+def test_rows_shared_by_the_two_ctas_of_a_cluster(path_override, shape, dtype, kind):
+    """Backward of rows beyond one CTA's register budget: each row is split over the two CTAs of
+    a thread-block cluster, which exchange their row sums through distributed shared memory.
+    The plan must be that one (half a row per 512 threads), the results the checker's, and two
+    runs must agree bit for bit (the order of every sum is fixed)."""
+    path_override(2)
+    rows, cols = shape
+    d = capi.describe_launch(True, rows, cols, dtype)
+    assert d["pipelined"] == 1 and d["threads_per_row"] == 512
+    assert 2 * d["vecs_per_thread"] * (d["vector_bytes"] // dtype.itemsize) * 512 == cols
+    x, gamma, beta, dy, _ = U.make_inputs(_seed(rows, cols) + 13, rows, cols, dtype)
+    f = O.norm_forward(x, gamma, None if kind == "rmsnorm" else beta, None, kind)
+    got = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind)
+    want = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, None, kind)
+    if dtype == F32:
+        torch.testing.assert_close(got["dx"], want["dx32"], rtol=1e-5, atol=1e-5)
+    else:
+        U.assert_out_close(got["dx"], want["dx"], dtype)
+    U.assert_param_grads_close(got["dgb_f32"][:cols], want["dgamma64"], want["abs64"][0], rows)
+    if kind == "layernorm":
+        U.assert_param_grads_close(got["dgb_f32"][cols:], want["dbeta64"], want["abs64"][1], rows)
+    again = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind)
+    assert torch.equal(got["dx"], again["dx"]) and torch.equal(got["dgb_f32"], again["dgb_f32"])
+    only_dx = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, want=(True, False, False), with_f32=False)
+    assert torch.equal(only_dx["dx"], got["dx"])
+    assert capi.lib().fln_device_status() == 0
 
 
 def test_pipelined_backward_adds_residual_gradient_in_place():
