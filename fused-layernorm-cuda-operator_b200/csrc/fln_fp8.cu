@@ -55,6 +55,10 @@ struct Fp8Params {
   float eps;
 };
 
+// Up to four vectors per thread the kernels fit 64 registers, i.e. 1024 threads per SM (one CTA
+// of 1024 or two of 512).  The four-vector form says so to the compiler (two CTAs per SM):
+// left alone, its MXFP8 instantiation took 66 registers and with that half the resident CTAs,
+// 428 instead of 372 us at 32768 x 8192.  Eight vectors per thread need more than 64.
 template <int K>
 struct Fp8MaxThreads {
   static constexpr int value = K <= 2 ? 1024 : 512;
@@ -137,7 +141,7 @@ __device__ __forceinline__ float row_max(float m, int tpr, float* smem) {
 // QMODE 0: phase 1 of the two-launch form (amax only); 1: quantize with *scale_in; 2: per-row
 // scale; 3: one E8M0 scale per block of 32 elements (MXFP8)
 template <typename TI, int VEC, int K, int KIND, bool FULL, int QMODE>
-__global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_amax_kernel(const Fp8Params p) {
+__global__ void __launch_bounds__(Fp8MaxThreads<K>::value, K == 4 ? 2 : 1) norm_amax_kernel(const Fp8Params p) {
   __shared__ __align__(16) float s_red[2][32];
   __shared__ float s_max[32];
   __shared__ float s_rmax[32];

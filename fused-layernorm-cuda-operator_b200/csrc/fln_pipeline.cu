@@ -109,9 +109,10 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // the 16-column plans; 24 columns spill a little and are slower than 12 (6144 columns: 3986
   // vs 5237 GB/s), but faster than the two-kernel long-row path (12288 columns: 4018 vs 3365
   // GB/s), so they serve only rows that fit no other plan.  fp32 backward stays at 16.
-  // Forward, 16-bit types: 40 elements per thread (K = 5 vectors of 8) with gamma / beta parked
-  // in shared memory instead of registers.
-  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : (elem_bytes == 2 && allow_params_in_smem ? 40 : 32),
+  // Forward, 16-bit types: 40 or 48 elements per thread (K = 5 or 6 vectors of 8) with gamma /
+  // beta parked in shared memory instead of registers.
+  const bool wide_fwd = !backward && elem_bytes == 2 && allow_params_in_smem;
+  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : (wide_fwd ? 48 : 32),
                        backward && elem_bytes == 2 ? 24 : 0};
   for (int pass = 0; pass < 2; ++pass) {
     const int cap_elems = caps[pass];
@@ -123,7 +124,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
       const int cvec = cvb / elem_bytes;
       if (cols % cvec != 0) continue;
       const int cnv = cols / cvec;
-      for (int ck = 3; ck <= 7; ck += 2) {
+      for (int ck = 3; ck <= 7; ++ck) {
+        if (ck == 4 || (ck == 6 && !(wide_fwd && cvb == 16))) continue;
         if (ck * cvec > cap_elems || cnv % ck != 0) continue;
         const int t = cnv / ck;
         if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;

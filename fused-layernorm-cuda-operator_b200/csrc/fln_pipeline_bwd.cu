@@ -472,14 +472,15 @@ static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) 
   constexpr int VEC = VB / (int)sizeof(T);
   if constexpr (VEC >= 2 && KK * VEC <= (sizeof(T) == 2 ? 24 : 16)) {
     const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
-    // geometry as template arguments for rows of 256 or 512 threads (no residual-stream gradient)
-    if (!dr && P.threads == 512 && (P.g.tpr == 512 || P.g.tpr == 256)) {
-      if (P.g.tpr == 512) {
-        if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, 9>, p, P, st);
-        return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, 9>, p, P, st);
-      }
-      if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, 8>, p, P, st);
-      return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, 8>, p, P, st);
+    // geometry as template arguments for rows of 64 to 512 threads (no residual-stream gradient)
+    if (!dr && P.threads == 512) {
+#define FLN_ODD_LT(L)                                                                                              \
+  if (P.g.tpr == (1 << L)) {                                                                                       \
+    if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, L>, p, P, st);     \
+    return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, L>, p, P, st);              \
+  }
+      FLN_ODD_LT(9) FLN_ODD_LT(8) FLN_ODD_LT(7) FLN_ODD_LT(6)
+#undef FLN_ODD_LT
     }
     if (fuse && dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB>, p, P, st);
     if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB>, p, P, st);

@@ -307,7 +307,8 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 template <typename TI, typename TO, int KIND, int ACT, int KK, int VB>
 static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = VB / (int)sizeof(TI);
-  constexpr int MODE = (VEC >= 4 && KK * VEC == 40 && sizeof(TI) == 2) ? 4 : ((VEC >= 4 && KK * VEC <= 32) ? 1 : -1);
+  constexpr int MODE =
+      (VEC >= 4 && KK * VEC > 32 && KK * VEC <= 48 && sizeof(TI) == 2) ? 4 : ((VEC >= 4 && KK * VEC <= 32) ? 1 : -1);
   if constexpr (MODE > 0) {
 #define FLN_GO(LTT)                                                             \
   {                                                                             \
@@ -337,11 +338,11 @@ static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) 
 
 template <typename TI, typename TO, int KIND, int ACT>
 static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
-  if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) {
+  if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) {
     if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_ODD(KK, VBB) \
   if (P.K == KK && P.vb == VBB) return fwd_pipe_odd<TI, TO, KIND, ACT, KK, VBB>(p, P, st);
-    FLN_ODD(3, 16) FLN_ODD(5, 16) FLN_ODD(7, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8)
+    FLN_ODD(3, 16) FLN_ODD(5, 16) FLN_ODD(6, 16) FLN_ODD(7, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8)
 #undef FLN_ODD
     return FLN_PIPE_NOT_APPLICABLE;
   }
