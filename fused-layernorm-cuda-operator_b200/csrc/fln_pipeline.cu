@@ -93,6 +93,9 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   for (int k = pref; k <= maxK && K == 0; k <<= 1) {
     int t = next_pow2i((nv + k - 1) / k);
     if (t > 512) continue;
+    // forward: two CTAs of 256 threads per SM rather than one of 512 while the register budget
+    // allows more vectors per thread (fp32 8192 columns: 8 vectors for each of 256 threads)
+    if (!backward && t > cta_threads && (k << 1) <= maxK) continue;
     if (t < 8) t = 8;
     int kk = next_pow2i((nv + t - 1) / t);
     K = kk;
@@ -125,7 +128,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
       if (cols % cvec != 0) continue;
       const int cnv = cols / cvec;
       for (int ck = 3; ck <= 7; ++ck) {
-        if (ck == 4 || (ck == 6 && !(wide_fwd && cvb == 16))) continue;
+        if (ck == 4 || (ck == 6 && (backward || cvb != 16))) continue;
         if (ck * cvec > cap_elems || cnv % ck != 0) continue;
         const int t = cnv / ck;
         if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
@@ -254,7 +257,7 @@ PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
   PipePlan P = backward ? plan_bwd_pipeline(rows, cols, elem_bytes, false) : plan_pipeline(false, rows, cols, elem_bytes, 1);
   if (!pipeline_wanted(P, rows)) return false;
-  if (!backward && elem_bytes == 4 && cols <= 12288 && g_path_override.load(std::memory_order_relaxed) == 0) {
+  if (!backward && elem_bytes == 4 && cols <= 4096 && g_path_override.load(std::memory_order_relaxed) == 0) {
     // the fp32 LayerNorm forward of short exact rows goes to the register kernel (launch_fwd_pipeline)
     const Plan rp = make_plan(false, rows, cols, elem_bytes, true);
     if (!rp.generic && rp.vec == 4 && (int64_t)rp.K * rp.tpr * rp.vec == cols) return false;

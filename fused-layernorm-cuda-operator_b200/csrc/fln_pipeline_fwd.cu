@@ -410,15 +410,19 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
   if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   // Measured exceptions (automatic selection only): fp32 rows that the non-persistent
   // register-resident kernel holds exactly stream faster there than through the ring -- a plain
-  // RMSNorm forward at every row length tried, the LayerNorm forward up to 12288 columns (8192:
-  // 5467 vs 4417 GB/s).  In 16-bit types the ring with its tiles handed out on demand is the
-  // faster one (RMSNorm 16384 x 8192 bf16: 84.1 vs 86.4 us).
+  // RMSNorm forward at every row length tried, the LayerNorm forward up to 4096 columns, where
+  // the ring runs 16 elements per thread (1024 / 2048 / 4096: 6743 / 6753 / 6658 vs 5651 / 5797 /
+  // 5504 GB/s; from 24 elements per thread the ring wins, 8192: 6651 vs 5497).  In 16-bit types
+  // the ring with its tiles handed out on demand is the faster one (RMSNorm 16384 x 8192 bf16:
+  // 84.1 vs 86.4 us).
   if (path_override() == 0 && p0.res == nullptr && act == FLN_ACT_NONE &&
       io_dtype == out_dtype) {
     const Plan rp = make_plan(false, p0.rows, p0.cols, es, true);
     const bool exact = !rp.generic && rp.vec == 16 / es && (int64_t)rp.K * rp.tpr * rp.vec == p0.cols;
-    if (kind == FLN_RMSNORM && !rp.generic && rp.vec == 16 / es && es == 4) return FLN_PIPE_NOT_APPLICABLE;
-    if (kind == FLN_LAYERNORM && es == 4 && exact && p0.cols <= 12288) return FLN_PIPE_NOT_APPLICABLE;
+    // (padded register plans of long rows excepted -- 6144 columns: 6188 vs 6707 GB/s)
+    if (kind == FLN_RMSNORM && !rp.generic && rp.vec == 16 / es && es == 4 && (exact || p0.cols <= 4096))
+      return FLN_PIPE_NOT_APPLICABLE;
+    if (kind == FLN_LAYERNORM && es == 4 && exact && p0.cols <= 4096) return FLN_PIPE_NOT_APPLICABLE;
   }
   FwdParams p = p0;
   p.nv = p.cols / (P.vb / es);
