@@ -70,7 +70,7 @@ static int next_pow2i(int v) {
 
 // tensors: how many input tensors are staged per tile (1 or 2)
 PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors,
-                       bool allow_params_in_smem) {
+                       bool allow_params_in_smem, bool allow_tail) {
   PipePlan P;
   memset(&P, 0, sizeof(P));
   const int vec = 16 / elem_bytes;
@@ -143,6 +143,29 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
       }
     }
   }
+  // Rows that fit none of the exact plans (1600 = 25 * 64 columns): K = 7 vectors on the
+  // power-of-two number of threads that leaves only the last vector ragged -- at most a seventh
+  // of the lanes idle in it, against up to half the lanes of the padded power-of-two plan -- in
+  // the widest vectors the register budget allows.  The kernels know at compile time that
+  // vectors 0 .. 5 are whole (the `tail` instantiations); rows must fill the CTA's row slots.
+  bool tail = false;
+  if (allow_tail && fK == 0 && tensors <= 2 && (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes))) {
+    const int cap_elems = backward ? (elem_bytes == 2 ? 20 : 16) : 32;
+    const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
+    for (int cvb = 16; cvb >= min_vb && !tail; cvb >>= 1) {
+      const int cvec = cvb / elem_bytes;
+      if (7 * cvec > cap_elems || cols % cvec != 0) continue;
+      const int cnv = cols / cvec;
+      const int t = next_pow2i((cnv + 6) / 7);
+      if (t < (backward ? 64 : 32) || t > 512 || (int64_t)6 * t >= cnv) continue;
+      const int thr = t > cta_threads ? t : cta_threads;
+      if (rows % (thr / t) != 0) continue;
+      K = 7;
+      tpr = t;
+      vb = cvb;
+      tail = true;
+    }
+  }
   if (K == 0) return P;
   const int threads = tpr > cta_threads ? tpr : cta_threads;
   const int R = threads / tpr;
@@ -174,6 +197,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   if (S > S_fit) S = S_fit;
   P.ok = true;
   P.full = tpr >= 32 && (int64_t)K * tpr == cols / (vb / elem_bytes) && rows % R == 0;
+  P.tail = tail;
   P.vb = vb;
   P.K = K;
   P.threads = threads;
@@ -184,7 +208,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
     if (S > room) S = room;
     // no room for two stages beside the parameters (two staged tensors of a long row): plan
     // again with at most 32 elements per thread
-    if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, false);
+    if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, false, allow_tail);
   }
   P.smem = kSmemHeader + (size_t)S * stage + (params_in_smem ? 2 * (size_t)row_bytes : 0);
   P.g.R = R;
@@ -263,7 +287,7 @@ bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, Pi
     if (!rp.generic && rp.vec == 4 && (int64_t)rp.K * rp.tpr * rp.vec == cols) return false;
   }
   // the odd plans exist only as branch-free instantiations; K = 8 only for fp32 forward
-  if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) && !P.full) return false;
+  if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) && !P.full && !P.tail) return false;
   out->vector_bytes = P.vb;
   out->K = P.K;
   out->tpr = P.g.tpr;
@@ -332,7 +356,9 @@ extern "C" int fln_planner_selftest(void) {
                       P.smem >= (size_t)kSmemHeader + (size_t)P.g.S * P.g.stage_stride;
             if (P.full) ok = ok && (int64_t)P.K * P.g.tpr * vec == cols && rows % P.g.R == 0;
             // odd K or short vectors exist only as branch-free instantiations
-            if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7) && !P.full) ok = false;
+            if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) && !P.full && !P.tail) ok = false;
+            // a ragged last vector: K = 7, vectors 0 .. 5 whole, rows fill the CTA
+            if (P.tail) ok = ok && P.K == 7 && !P.full && (int64_t)6 * P.g.tpr < cols / vec && rows % P.g.R == 0;
             if (!ok) ++bad;
           }
   return bad;

@@ -243,6 +243,7 @@ struct PipePlan {
   bool ok;
   bool full;  // branch-free instantiation applies
   bool pair;  // backward only: a row is shared by the two CTAs of a cluster (each half a row)
+  bool tail;  // rows are whole but the last of a thread's K vectors is ragged (lanes beyond the row idle)
   int vb;     // bytes per vector: 16, or 8 / 4 where that makes the row divide evenly
   int K;
   int threads;
@@ -253,7 +254,7 @@ struct PipePlan {
 
 // tensors: how many input tensors are staged per tile (forward 1 or 2, backward 2 or 3)
 PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors,
-                       bool allow_params_in_smem = true);
+                       bool allow_params_in_smem = true, bool allow_tail = true);
 PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres);
 bool pipeline_wanted(const PipePlan& P, int64_t rows);
 int path_override();                  // fln_set_path_override

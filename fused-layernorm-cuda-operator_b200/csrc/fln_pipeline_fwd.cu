@@ -24,6 +24,9 @@ namespace fln {
 // registers as floats, for plans that give a thread more than 32 elements (row lengths
 // 5 * 2^a in 16-bit types: 40 elements per thread keep the 16-byte vectors and move more
 // bytes per barrier than 20 elements in 8-byte vectors)
+// MODE 5: rows whole, every vector whole except the last of a thread's K (rows that fit no
+// exact plan, 1600 columns: K = 7, lanes beyond the row idle in the seventh vector only); the
+// row length comes from the launch parameters, the split from LT.
 // LT >= 0: the geometry is known at compile time -- a CTA of 256 threads (512 for LT = 9), 2^LT threads per row,
 // rows of exactly K * VEC * 2^LT elements (FULL).  Row length, byte offsets of a thread's
 // vectors and the shape of the reductions then fold into immediates: the bf16 forward at
@@ -35,15 +38,19 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   constexpr int V2 = VEC / 2;
   constexpr bool FULL = MODE >= 1;
   constexpr bool PSM = MODE == 4;
+  constexpr bool TAIL = MODE == 5;
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
-  static_assert(!CT || MODE == 1 || MODE == 4, "compile-time geometry is for the FULL kernels");
+  static_assert(!CT || MODE == 1 || MODE == 4 || MODE == 5, "compile-time geometry is for the FULL kernels");
+  static_assert(!TAIL || CT, "the ragged-last-vector kernel has its split at compile time");
+// vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
+#define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
   const int tpr = CT ? (1 << LTC) : g.tpr;
   const int log2_tpr = CT ? LTC : g.log2_tpr;
   const int R = CT ? (NT >> LTC) : g.R;
-  const int cols = CT ? ((K * VEC) << LTC) : p.cols;
-  const uint32_t row_bytes = CT ? (uint32_t)((K * VB) << LTC) : g.row_bytes;
+  const int cols = (CT && !TAIL) ? ((K * VEC) << LTC) : p.cols;
+  const uint32_t row_bytes = (CT && !TAIL) ? (uint32_t)((K * VB) << LTC) : g.row_bytes;
   const uint32_t second_off = CT ? row_bytes * (uint32_t)R : g.second_off;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -102,7 +109,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    vok[k] = FULL ? true : iv < p.nv;
+    vok[k] = FLN_WHOLE(k) ? true : iv < p.nv;
     if constexpr (PSM) {
       if (r_in == 0) {
         Pack<TI, VEC> one, zero;
@@ -152,7 +159,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     float2 f[K][V2];
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      if (FULL || (row_ok && vok[k])) {
+      if (FLN_WHOLE(k) || (row_ok && vok[k])) {
         unpack2<TI, VEC>(stage_vec<TI, VEC>(st + k * k_off), f[k]);
       } else {
 #pragma unroll
@@ -163,7 +170,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       TI* __restrict__ sr = reinterpret_cast<TI*>(p.sum_out) + row * (int64_t)cols + (int64_t)lane_r * VEC;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        if (FULL || (row_ok && vok[k])) {
+        if (FLN_WHOLE(k) || (row_ok && vok[k])) {
           float2 r[V2];
           unpack2<TI, VEC>(stage_vec<TI, VEC>(st + second_off + k * k_off), r);
 #pragma unroll
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       float2 a01 = f2(0.f), a23 = f2(0.f);  // four chains: the adds are latency-bound
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        if (FULL || vok[k]) {  // padding vectors stay zero
+        if (FLN_WHOLE(k) || vok[k]) {  // padding vectors stay zero
 #pragma unroll
           for (int e = 0; e < V2; e += 2) {
             f[k][e] = f2add(f[k][e], nc);
@@ -217,7 +224,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       const float2 nms = f2(-ms);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        if (FULL || vok[k]) {
+        if (FLN_WHOLE(k) || vok[k]) {
 #pragma unroll
           for (int e = 0; e < V2; ++e) f[k][e] = f2add(f[k][e], nms);
         }
@@ -257,7 +264,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     const float2 r2 = f2(rstd);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      if (FULL || (row_ok && vok[k])) {
+      if (FLN_WHOLE(k) || (row_ok && vok[k])) {
         float2 o[V2];
         if constexpr (PSM) {
           float2 gw[V2], bw[V2];
@@ -300,6 +307,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     }
   }
 }
+#undef FLN_WHOLE
 
 // one branch-free instantiation with an odd K and / or short vectors; combinations that make no
 // sense for the type (too many elements per thread, vectors shorter than four elements) are
@@ -336,8 +344,31 @@ static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) 
   }
 }
 
+// rows whose last vector is ragged (plan_pipeline's `tail` plans): K = 7 vectors of 8 bytes
+// (16-bit types) or 16 bytes (fp32); plain forward only
+template <typename TI, typename TO, int KIND, int ACT>
+static int fwd_pipe_tail(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
+    constexpr int VB = sizeof(TI) == 2 ? 8 : 16;
+    const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
+    if (P.K != 7 || P.vb != VB || P.threads != nt) return FLN_PIPE_NOT_APPLICABLE;
+#define FLN_GO(LTT)                                                          \
+  if (P.g.tpr == (1 << LTT)) {                                               \
+    auto kern = norm_fwd_pipe_kernel<TI, TO, 7, KIND, ACT, 5, VB, LTT>;      \
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;             \
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                         \
+    FLN_CHECK_LAUNCH();                                                      \
+    return FLN_OK;                                                           \
+  }
+    FLN_GO(5) FLN_GO(6) FLN_GO(7) FLN_GO(8) FLN_GO(9)
+#undef FLN_GO
+  }
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
 template <typename TI, typename TO, int KIND, int ACT>
 static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (P.tail) return fwd_pipe_tail<TI, TO, KIND, ACT>(p, P, st);
   if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) {
     if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_ODD(KK, VBB) \
@@ -406,7 +437,9 @@ static int fwd_pipe_typed(int kind, int act, const FwdParams& p, const PipePlan&
 int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p0,
                         cudaStream_t st) {
   const int es = io_dtype == FLN_F32 ? 4 : 2;
-  PipePlan P = plan_pipeline(false, p0.rows, p0.cols, es, p0.res != nullptr ? 2 : 1);
+  // the ragged-last-vector plans exist for the plain forward only
+  const bool allow_tail = act == FLN_ACT_NONE && io_dtype == out_dtype;
+  PipePlan P = plan_pipeline(false, p0.rows, p0.cols, es, p0.res != nullptr ? 2 : 1, true, allow_tail);
   if (!pipeline_wanted(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   // Measured exceptions (automatic selection only): fp32 rows that the non-persistent
   // register-resident kernel holds exactly stream faster there than through the ring -- a plain

@@ -662,6 +662,52 @@ def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape,
     assert capi.lib().fln_device_status() == 0
 
 
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype", [BF16, F32, F16])
+@pytest.mark.parametrize("shape", [(4096, 1600), (1024, 1664), (2048, 800), (512, 3200), (256, 6400), (128, 12800),
+                                   (4098, 1600)])
+def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
+    """Row lengths that fit no exact plan (1600 = 25 * 64): seven vectors per thread of which only
+    the last is ragged.  The plan must be that one where the rows fill the CTA's row slots (4098
+    rows do not: the padded plan runs), results the checker's, forward with and without a
+    residual, backward with and without the incoming residual-stream gradient (the latter on
+    the padded plan), two backward runs bit-identical."""
+    path_override(2)
+    rows, cols = shape
+    for backward in (False, True):
+        d = capi.describe_launch(backward, rows, cols, dtype)
+        if rows != 4098 and (not backward or cols <= 7168):  # 14 columns for each of up to 512 threads
+            assert d["pipelined"] == 1 and d["vecs_per_thread"] == 7
+            nv = cols // (d["vector_bytes"] // dtype.itemsize)
+            assert 6 * d["threads_per_row"] < nv <= 7 * d["threads_per_row"]
+    x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 17, rows, cols, dtype, residual=True)
+    if kind == "rmsnorm":
+        beta = None
+    for r in (None, res):
+        got = U.run_forward(x, gamma, beta, r, kind)
+        want = O.norm_forward(x, gamma, beta, r, kind)
+        U.assert_out_close(got["y"], want["y"], dtype)
+        torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+        if kind == "layernorm":
+            torch.testing.assert_close(got["mean"], want["mean"], rtol=1e-5, atol=1e-5)
+        if r is not None:
+            assert torch.equal(got["sum"].view(torch.uint8), want["sum"].view(torch.uint8))
+    f = O.norm_forward(x, gamma, beta, None, kind)
+    for dres in (None, res):
+        gb = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        wb = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, dres, kind)
+        if dtype == F32:
+            torch.testing.assert_close(gb["dx"], wb["dx32"], rtol=1e-5, atol=1e-5)
+        else:
+            U.assert_out_close(gb["dx"], wb["dx"], dtype)
+        U.assert_param_grads_close(gb["dgb_f32"][:cols], wb["dgamma64"], wb["abs64"][0], rows)
+        if kind == "layernorm":
+            U.assert_param_grads_close(gb["dgb_f32"][cols:], wb["dbeta64"], wb["abs64"][1], rows)
+        again = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        assert torch.equal(gb["dx"], again["dx"]) and torch.equal(gb["dgb_f32"], again["dgb_f32"])
+    assert capi.lib().fln_device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(1536, 1280), (600, 5120), (304, 6144), (512, 8192)])
 def test_pipelined_forward_without_parameters(path_override, shape):
     """elementwise_affine=False through the pipelined kernels, including the plan that keeps
