@@ -239,19 +239,23 @@ def small_shape_latency(torch, capi):
     from fused_layernorm.graphs import GraphedLayerNorm
     L = capi.lib()
 
-    def loop_us(fn, calls_per_iter=1):
-        for _ in range(200):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(1000):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / calls_per_iter  # ms per 1000 iterations == us per iteration
+    def loop_us(fn, args=(), calls_per_iter=1):
+        best = float("inf")
+        for _ in range(3):
+            for _ in range(200):
+                fn(*args)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(1000):
+                fn(*args)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / calls_per_iter)  # ms per 1000 iterations == us per iteration
+        return best
 
-    out = {"protocol": "same-tensor loop, 200 warm-up + 1000 timed calls, us per call"}
+    out = {"protocol": "same-tensor loop, 200 warm-up + 1000 timed calls, best of 3, us per call (the protocol of the "
+                       "reference arm's reference_cuda_kernel_small_shape)"}
     shapes = [(48, 512, torch.float32)] + [(32, 768, torch.float32)] + \
              [(r, c, dt) for dt in (torch.float32, torch.bfloat16)
               for r, c in ((32, 1024), (32, 4096), (64, 4096), (17, 1023))]
@@ -266,13 +270,13 @@ def small_shape_latency(torch, capi):
         g20 = GraphedLayerNorm(x, w, b, 1e-5, repeat=20)
         gg = GraphedLayerNorm(x, w, b, 1e-5, gelu="tanh", repeat=20)
         rec = {
-            "ours_pybind": loop_us(lambda: ext.layernorm(x, w, b, 1e-5)),
-            "ours_pybind_gelu": loop_us(lambda: ext.layernorm_gelu(x, w, b, 1e-5)),
-            "ours_c_abi": loop_us(lambda: L.fln_layernorm_forward(px, pw, pb, py, None, None, rows, cols, code, 1e-5, st)),
-            "ours_graph": loop_us(lambda: g1()),
-            "ours_graph_x20": loop_us(lambda: g20(), 20),
-            "ours_graph_x20_gelu": loop_us(lambda: gg(), 20),
-            "torch_cuda": loop_us(lambda: F.layer_norm(x, (cols,), w, b, 1e-5)),
+            "ours_pybind": loop_us(ext.layernorm, (x, w, b, 1e-5)),
+            "ours_pybind_gelu": loop_us(ext.layernorm_gelu, (x, w, b, 1e-5)),
+            "ours_c_abi": loop_us(L.fln_layernorm_forward, (px, pw, pb, py, None, None, rows, cols, code, 1e-5, st)),
+            "ours_graph": loop_us(g1),
+            "ours_graph_x20": loop_us(g20, (), 20),
+            "ours_graph_x20_gelu": loop_us(gg, (), 20),
+            "torch_cuda": loop_us(F.layer_norm, (x, (cols,), w, b, 1e-5)),
         }
         for g in (g1, g20, gg):
             g.close()

@@ -14,6 +14,7 @@
 // TORCH_CHECK -> RuntimeError; unsupported dtypes -> NotImplementedError like its
 // AT_DISPATCH macro.  There is no CPU path.
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/EmptyTensor.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/autograd.h>
 #include <torch/extension.h>
@@ -83,6 +84,22 @@ Tensor check_stat(const Tensor& t, const Tensor& x, const char* name) {
   return t.contiguous();
 }
 
+// Outputs and scratch straight from the caching allocator.  (at::empty / at::empty_like go
+// through the dispatcher first: 1.27 instead of 0.87 us per tensor, a tenth of a whole call at
+// the latency-bound shapes.)
+Tensor new_cuda(at::IntArrayRef sizes, at::ScalarType dtype, const Tensor& on_device_of) {
+  return Tensor(at::detail::empty_cuda(sizes, dtype, on_device_of.device(), std::nullopt));
+}
+Tensor new_like(const Tensor& x) { return new_cuda(x.sizes(), x.scalar_type(), x); }
+
+// makes x's device current for the launch; nothing to undo in the usual case that it already is
+struct DeviceOf {
+  std::optional<c10::cuda::CUDAGuard> guard;
+  explicit DeviceOf(const Tensor& x) {
+    if (c10::cuda::current_device() != x.device().index()) guard.emplace(x.device());
+  }
+};
+
 void* stream_of(const Tensor& x) { return at::cuda::getCurrentCUDAStream(x.get_device()).stream(); }
 
 int act_code(const std::string& approximate) {
@@ -103,7 +120,7 @@ FwdOut norm_forward(int kind, const Tensor& input, const OptTensor& residual, co
                     const OptTensor& beta, double eps, int act, bool want_stats, const char* op) {
   Tensor x = check_matrix(input, "input");
   const int dt = dtype_code(x, op);
-  c10::cuda::CUDAGuard guard(x.device());
+  DeviceOf guard(x);
   Tensor gk, bk, rk;
   const void* g = param_ptr(gamma, x, "Gamma", gk);
   const void* b = param_ptr(beta, x, "Beta", bk);
@@ -113,19 +130,18 @@ FwdOut norm_forward(int kind, const Tensor& input, const OptTensor& residual, co
   if (residual.has_value() && residual->defined()) {
     rk = check_like(*residual, x, "residual");
     r = rk.data_ptr();
-    o.sum = at::empty_like(x);
+    o.sum = new_like(x);
     s = o.sum.data_ptr();
   }
-  o.y = at::empty_like(x);
+  o.y = new_like(x);
   float* mean = nullptr;
   float* rstd = nullptr;
   if (want_stats) {
-    auto so = x.options().dtype(at::kFloat);
     if (kind == FLN_LAYERNORM) {
-      o.mean = at::empty({x.size(0)}, so);
+      o.mean = new_cuda({x.size(0)}, at::kFloat, x);
       mean = o.mean.data_ptr<float>();
     }
-    o.rstd = at::empty({x.size(0)}, so);
+    o.rstd = new_cuda({x.size(0)}, at::kFloat, x);
     rstd = o.rstd.data_ptr<float>();
   }
   check_status(fln_norm_forward(kind, x.data_ptr(), r, g, b, o.y.data_ptr(), s, mean, rstd, x.size(0), x.size(1), dt,
@@ -173,7 +189,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> norm_fp8(int64_t kind, const 
   TORCH_CHECK(kind == FLN_LAYERNORM || kind == FLN_RMSNORM, "kind must be 0 (layernorm) or 1 (rmsnorm)");
   Tensor x = check_matrix(input, "input");
   const int dt = dtype_code(x, "norm_fp8");
-  c10::cuda::CUDAGuard guard(x.device());
+  DeviceOf guard(x);
   Tensor gk, bk, rk, sum, mean;
   const void* g = param_ptr(gamma, x, "Gamma", gk);
   const void* b = param_ptr(beta, x, "Beta", bk);
@@ -183,16 +199,15 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> norm_fp8(int64_t kind, const 
   if (residual.has_value() && residual->defined()) {
     rk = check_like(*residual, x, "residual");
     r = rk.data_ptr();
-    sum = at::empty_like(x);
+    sum = new_like(x);
     s = sum.data_ptr();
   } else {
-    sum = at::empty({0}, x.options());
+    sum = new_cuda({0}, x.scalar_type(), x);
   }
-  auto so = x.options().dtype(at::kFloat);
-  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
-  Tensor rstd = at::empty({x.size(0)}, so);
-  mean = kind == FLN_LAYERNORM ? at::empty({x.size(0)}, so) : at::empty({0}, so);
-  Tensor amax_scale = at::empty({2}, so);
+  Tensor q = new_cuda(x.sizes(), at::kFloat8_e4m3fn, x);
+  Tensor rstd = new_cuda({x.size(0)}, at::kFloat, x);
+  mean = kind == FLN_LAYERNORM ? new_cuda({x.size(0)}, at::kFloat, x) : new_cuda({0}, at::kFloat, x);
+  Tensor amax_scale = new_cuda({2}, at::kFloat, x);
   float* as = amax_scale.data_ptr<float>();
   check_status(fln_norm_forward_fp8((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), s,
                                     kind == FLN_LAYERNORM ? mean.data_ptr<float>() : nullptr, rstd.data_ptr<float>(), as,
@@ -210,7 +225,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_fp8_scaled(int64_t kind, const T
   TORCH_CHECK(kind == FLN_LAYERNORM || kind == FLN_RMSNORM, "kind must be 0 (layernorm) or 1 (rmsnorm)");
   Tensor x = check_matrix(input, "input");
   const int dt = dtype_code(x, "norm_fp8_scaled");
-  c10::cuda::CUDAGuard guard(x.device());
+  DeviceOf guard(x);
   Tensor gk, bk, rk, sum, sk;
   const void* g = param_ptr(gamma, x, "Gamma", gk);
   const void* b = param_ptr(beta, x, "Beta", bk);
@@ -220,14 +235,13 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_fp8_scaled(int64_t kind, const T
   if (residual.has_value() && residual->defined()) {
     rk = check_like(*residual, x, "residual");
     r = rk.data_ptr();
-    sum = at::empty_like(x);
+    sum = new_like(x);
     s = sum.data_ptr();
   } else {
-    sum = at::empty({0}, x.options());
+    sum = new_cuda({0}, x.scalar_type(), x);
   }
-  auto so = x.options().dtype(at::kFloat);
-  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
-  Tensor amax = at::empty({1}, so);
+  Tensor q = new_cuda(x.sizes(), at::kFloat8_e4m3fn, x);
+  Tensor amax = new_cuda({1}, at::kFloat, x);
   const bool delayed = scale_in.has_value() && scale_in->defined();
   if (delayed) {
     TORCH_CHECK(scale_in->is_cuda() && scale_in->device() == x.device() && scale_in->scalar_type() == at::kFloat &&
@@ -238,9 +252,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_fp8_scaled(int64_t kind, const T
                                               sk.data_ptr<float>(), amax.data_ptr<float>(), x.size(0), x.size(1), dt,
                                               (float)epsilon, stream_of(x)),
                  "norm_fp8_scaled");
-    return {q, sum, at::empty({0}, so), amax};
+    return {q, sum, new_cuda({0}, at::kFloat, x), amax};
   }
-  Tensor row_scale = at::empty({x.size(0)}, so);
+  Tensor row_scale = new_cuda({x.size(0)}, at::kFloat, x);
   check_status(fln_norm_forward_fp8_rowwise((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), s, nullptr, nullptr,
                                             row_scale.data_ptr<float>(), amax.data_ptr<float>(), x.size(0), x.size(1),
                                             dt, (float)epsilon, stream_of(x)),
@@ -255,7 +269,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_mxfp8(int64_t kind, const Tensor
   Tensor x = check_matrix(input, "input");
   TORCH_CHECK(x.size(1) % 32 == 0, "mxfp8 output needs a row length that is a multiple of 32");
   const int dt = dtype_code(x, "norm_mxfp8");
-  c10::cuda::CUDAGuard guard(x.device());
+  DeviceOf guard(x);
   Tensor gk, bk, rk, sum;
   const void* g = param_ptr(gamma, x, "Gamma", gk);
   const void* b = param_ptr(beta, x, "Beta", bk);
@@ -265,14 +279,14 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> norm_mxfp8(int64_t kind, const Tensor
   if (residual.has_value() && residual->defined()) {
     rk = check_like(*residual, x, "residual");
     r = rk.data_ptr();
-    sum = at::empty_like(x);
+    sum = new_like(x);
     s = sum.data_ptr();
   } else {
-    sum = at::empty({0}, x.options());
+    sum = new_cuda({0}, x.scalar_type(), x);
   }
-  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
-  Tensor scales = at::empty({x.size(0), x.size(1) / 32}, x.options().dtype(at::kByte));
-  Tensor amax = at::empty({1}, x.options().dtype(at::kFloat));
+  Tensor q = new_cuda(x.sizes(), at::kFloat8_e4m3fn, x);
+  Tensor scales = new_cuda({x.size(0), x.size(1) / 32}, at::kByte, x);
+  Tensor amax = new_cuda({1}, at::kFloat, x);
   check_status(fln_norm_forward_mxfp8((int)kind, x.data_ptr(), r, g, b, q.data_ptr(), scales.data_ptr<uint8_t>(), s,
                                       nullptr, nullptr, amax.data_ptr<float>(), x.size(0), x.size(1), dt,
                                       (float)epsilon, stream_of(x)),
@@ -294,7 +308,7 @@ BwdOut norm_backward(int kind, const Tensor& grad_output, const Tensor& input, c
   TORCH_CHECK(grad_output.device().is_cuda(), "grad_output must be a CUDA tensor");
   TORCH_CHECK(grad_output.sizes() == x.sizes(), "grad_output shape must match input shape");
   const int dt = dtype_code(x, op);
-  c10::cuda::CUDAGuard guard(x.device());
+  DeviceOf guard(x);
   Tensor dy = check_like(grad_output, x, "grad_output");
   Tensor rstd = check_stat(rstd_t, x, "rstd");
   Tensor mean, gk, dk;
@@ -313,15 +327,15 @@ BwdOut norm_backward(int kind, const Tensor& grad_output, const Tensor& input, c
   }
   const int64_t rows = x.size(0), cols = x.size(1);
   BwdOut o;
-  if (want_dx) o.dx = at::empty_like(x);
-  if (want_dgamma) o.dgamma = at::empty({cols}, x.options());
-  if (want_dbeta && kind == FLN_LAYERNORM) o.dbeta = at::empty({cols}, x.options());
-  if (want_f32) o.dgb_f32 = at::empty({(kind == FLN_LAYERNORM ? 2 : 1) * cols}, x.options().dtype(at::kFloat));
+  if (want_dx) o.dx = new_like(x);
+  if (want_dgamma) o.dgamma = new_cuda({cols}, x.scalar_type(), x);
+  if (want_dbeta && kind == FLN_LAYERNORM) o.dbeta = new_cuda({cols}, x.scalar_type(), x);
+  if (want_f32) o.dgb_f32 = new_cuda({(kind == FLN_LAYERNORM ? 2 : 1) * cols}, at::kFloat, x);
   Tensor ws;
   size_t ws_bytes = 0;
   if (o.dgamma.defined() || o.dbeta.defined() || o.dgb_f32.defined()) {
     ws_bytes = fln_backward_workspace_bytes(rows, cols, dt);
-    if (ws_bytes > 0) ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+    if (ws_bytes > 0) ws = new_cuda({(int64_t)ws_bytes}, at::kByte, x);
   }
   check_status(fln_norm_backward(kind, dy.data_ptr(), x.data_ptr(), mean_p, rstd.data_ptr<float>(), g, dr,
                                  o.dx.defined() ? o.dx.data_ptr() : nullptr,
@@ -333,7 +347,7 @@ BwdOut norm_backward(int kind, const Tensor& grad_output, const Tensor& input, c
   return o;
 }
 
-Tensor or_empty(const Tensor& t, const Tensor& like) { return t.defined() ? t : at::empty({0}, like.options()); }
+Tensor or_empty(const Tensor& t, const Tensor& like) { return t.defined() ? t : new_cuda({0}, like.scalar_type(), like); }
 
 // operator forms: masked-off gradients come back as empty (0-element) tensors
 std::tuple<Tensor, Tensor, Tensor> layernorm_bwd(const Tensor& grad_output, const Tensor& input, const Tensor& mean,
@@ -359,9 +373,9 @@ std::tuple<Tensor, Tensor> layernorm_bwd_f32(const Tensor& grad_output, const Te
 }
 Tensor cast_from_f32(const Tensor& src, at::ScalarType dtype) {
   TORCH_CHECK(src.device().is_cuda() && src.scalar_type() == at::kFloat, "src must be a CUDA float32 tensor");
-  c10::cuda::CUDAGuard guard(src.device());
+  DeviceOf guard(src);
   Tensor s = src.contiguous();
-  Tensor out = at::empty(s.sizes(), s.options().dtype(dtype));
+  Tensor out = new_cuda(s.sizes(), dtype, s);
   check_status(fln_cast_from_f32(s.data_ptr<float>(), out.data_ptr(), s.numel(), dtype_code(out, "cast_from_f32"),
                                  stream_of(s)),
                "cast_from_f32");
@@ -443,7 +457,7 @@ struct NormAutograd : public torch::autograd::Function<NormAutograd> {
     ctx->saved_data["i_res"] = has_r ? next++ : (int64_t)-1;
     ctx->saved_data["i_g"] = has_g ? next++ : (int64_t)-1;
     ctx->saved_data["i_b"] = has_b ? next++ : (int64_t)-1;
-    return {o.y, has_r ? o.sum : at::empty({0}, input.options())};
+    return {o.y, has_r ? o.sum : new_cuda({0}, input.scalar_type(), input)};
   }
   static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
                                                torch::autograd::tensor_list grads) {
