@@ -7,7 +7,7 @@ this prints which one served each shape (`fln_describe_launch`) beside the rate,
 CUDA LayerNorm forward for comparison.  GB/s counts every input read once and every output
 written once (forward 2 tensors, backward 3).
 
-    python hidden_size_sweep.py [--dtypes bfloat16,float32] [--mib 512] [--json out.json]
+    python hidden_size_sweep.py [--dtypes bfloat16,float32] [--hidden 1600,8192] [--mib 512] [--json out.json]
 """
 from __future__ import annotations
 
@@ -54,13 +54,15 @@ def main():
     ap.add_argument("--path-override", type=int, default=0,
                     help="fln_set_path_override: 0 automatic, 1 register kernels only, 2 pipeline wherever it fits")
     ap.add_argument("--skip-torch", action="store_true")
+    ap.add_argument("--hidden", default=None, help="comma-separated hidden sizes instead of the built-in list")
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     capi.lib().fln_set_path_override(args.path_override)
     out = []
     for dn in args.dtypes.split(","):
         dt = getattr(torch, dn)
         es = dt.itemsize
-        for cols in HIDDEN:
+        for cols in (HIDDEN if args.hidden is None else tuple(int(h) for h in args.hidden.split(","))):
             rows = (args.mib * 1024 * 1024 // es // cols) // 64 * 64
             x = torch.randn(rows, cols, device="cuda", dtype=dt)
             dy = torch.randn_like(x)
@@ -70,8 +72,8 @@ def main():
             mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
             dg, db = torch.empty_like(g), torch.empty_like(g)
             ws = torch.empty(max(capi.backward_workspace_bytes(rows, cols, dt) // 4, 1), device="cuda")
-            tf = loop_us(lambda: capi.layernorm_forward(x, g, b, y, mean, rstd, 1e-5))
-            tb = loop_us(lambda: capi.layernorm_backward(dy, x, mean, rstd, g, dx, dg, db, ws))
+            tf = loop_us(lambda: capi.layernorm_forward(x, g, b, y, mean, rstd, 1e-5), iters=args.iters)
+            tb = loop_us(lambda: capi.layernorm_backward(dy, x, mean, rstd, g, dx, dg, db, ws), iters=args.iters)
             tt = float('inf') if args.skip_torch else loop_us(lambda: F.layer_norm(x, (cols,), g, b, 1e-5))
             nb = rows * cols * es
             rec = {"dtype": dn, "rows": rows, "hidden": cols, "fwd_us": tf, "fwd_gbs": 2 * nb / tf / 1e3,
