@@ -140,8 +140,13 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+// one float into another CTA's shared memory, counted as four bytes of transaction on an
+// mbarrier of that CTA: the receiver's wait on that barrier makes the value visible, and the
+// sender needs no fence (a release fence here would also wait for the sender's global stores)
+__device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr),
+               "r"(__float_as_uint(v)), "r"(mbar)
+               : "memory");
 }
 // One 16-byte vector of a stage as ONE 128-bit shared-memory load.  (Handing the stage to the
 // conversion helper by reference lets the compiler read it word by word: four times the load

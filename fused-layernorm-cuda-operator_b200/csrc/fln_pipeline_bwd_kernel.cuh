@@ -115,12 +115,13 @@ __device__ __noinline__ void fused_column_reduce(const ReduceArgs p, float* sb, 
 // PAIR: launched as clusters of two CTAs that share every row: CTA `rank` of the cluster stages
 // and differentiates columns [rank * cols, rank * cols + cols) of a row of 2 * cols (cols = the
 // half row, K * VEC * 512: one row per tile, 512 threads per half row).  The two partial row
-// sums of each CTA's 16 warps go into the partner's shared memory as well (st.shared::cluster);
-// the hardware cluster barrier takes the place of the CTA barrier of every row (it releases
-// the stage and publishes the sums), and both CTAs add the 32 values of a sum in the same
-// order.  The cluster barrier has no bounded form, so no CTA may skip one: a CTA whose wait for
-// a copy ran out flags it, stops working and keeps meeting its partner at the barrier for the
-// rows that remain (both CTAs of a cluster have the same number of rows).
+// sums of each CTA's 16 warps go into the partner's shared memory as well, by st.async counted
+// on an mbarrier of the partner (two of them, rows alternate): a CTA waits -- bounded like every
+// wait here -- for the partner's 16 x NR values of the row, then meets its own threads at the
+// CTA barrier as every other instantiation does, and both CTAs add the 32 values of a sum in
+// the same order.  Nothing in the row loop fences: the cluster barrier (arrive.release) that
+// an earlier form used per row also waited for the dx stores of the row before, 0.5 us a row.
+// A CTA that gives up stops sending; its partner's wait then runs out as well.
 // TAIL: rows whole, every vector whole except the last of a thread's K (rows that fit no exact
 // plan, 1600 columns); the row length comes from the launch parameters, the split from LT.
 template <typename T, int K, int KIND, bool FULL, bool FUSE, bool DRES, int VB = 16, int LT = -1, bool PAIR = false,
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   const uint32_t stage_stride = CT ? second_off * (uint32_t)NPROD : g.stage_stride;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  int* pair_flag = reinterpret_cast<int*>(smem + 192);  // PAIR: set by a thread whose wait for a copy ran out
+  uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + 192);  // PAIR: the partner's sums of even / odd rows land here
   float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 floats (PAIR: 2 x [2 ranks][64])
   unsigned char* stages = smem + kSmemHeader;
 
@@ -173,8 +174,15 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) mbar_init(&full[s], NPROD);
-    if (PAIR) *reinterpret_cast<volatile int*>(pair_flag) = 0;
+    if (PAIR) {
+      mbar_init(&xbar[0], 1);
+      mbar_init(&xbar[1], 1);
+    }
     mbar_init_fence();
+    if (PAIR) {
+      mbar_expect_tx(&xbar[0], 16u * NR * 4u);
+      mbar_expect_tx(&xbar[1], 16u * NR * 4u);
+    }
   }
   if (FUSE && tid == 96) grid_barrier_init(p.sync, p.token);
   if (PAIR) cluster_sync_all();  // the partner's barriers exist before anything remote happens
@@ -290,19 +298,21 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
       if ((tid & 31) == 0) {
         float* mine = sr + rank * 64 + (tid >> 5);
         const uint32_t theirs = map_to_cta(mine, rank ^ 1u);
+        const uint32_t their_bar = map_to_cta(&xbar[i & 1], rank ^ 1u);
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
           mine[n * 32] = red[n];
-          st_cluster_f32(theirs + n * 32 * 4, red[n]);
+          st_async_f32(theirs + n * 32 * 4, red[n], their_bar);
         }
       }
-      if (!landed) *reinterpret_cast<volatile int*>(pair_flag) = 1;
-      cluster_arrive();
-      cluster_wait();
-      if (*reinterpret_cast<volatile int*>(pair_flag) != 0) {
+      const bool theirs_landed = mbar_wait_bounded(&xbar[i & 1], (uint32_t)(i >> 1) & 1u, p.wait_ns);
+      if (!__syncthreads_and(landed && theirs_landed ? 1 : 0)) {
         aborted = true;
         break;
       }
+      // the partner sends row i + 2 only after it has this CTA's row i + 1, which every warp
+      // here sends after reading the sums of row i: the table and the barrier are free again
+      if (tid == 0 && i + 2 < my_tiles) mbar_expect_tx(&xbar[i & 1], 16u * NR * 4u);
       if (is_producer && i + S < my_tiles) issue(i + S, s, false);
 #pragma unroll
       for (int n = 0; n < NR; ++n) red[n] = sum_w<16>(sr + n * 32) + sum_w<16>(sr + 64 + n * 32);
@@ -361,10 +371,6 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
     }
   }
   if (aborted && tid == 0) pipeline_abort(p.status, full, S, s, phase, my_tiles - i < S ? my_tiles - i : S, p.wait_ns);
-  if (PAIR && aborted) {
-    // keep the partner company at the barriers of the rows this CTA no longer works on
-    for (int j = i + 1; j < my_tiles; ++j) cluster_sync_all();
-  }
 
   if (p.partials != nullptr && !aborted) {
     const int64_t prow = (int64_t)FLN_SLOT * R + r_in;
