@@ -142,3 +142,38 @@ def test_forward_stage_wait_gives_up_and_the_next_call_is_correct(hooks):
         assert hooks.fln_device_status() == 0
         U.assert_out_close(y.cpu(), f["y"], BF16)
         torch.testing.assert_close(mean.cpu(), f["mean"], rtol=1e-5, atol=1e-5)
+
+
+def test_cluster_pair_gives_up_together_and_the_next_call_is_correct(hooks):
+    """A row shared by the two CTAs of a cluster: CTA 0 never gets its first copy, so its wait
+    runs out; its partner then waits in vain for CTA 0's row sums and gives up too (that wait is
+    bounded like the others).  Both leave through the ordinary exit, the status word says 1,
+    and the next call is correct."""
+    rows, cols = 600, 16384
+    F32 = torch.float32
+    hooks.fln_set_path_override(2)
+    try:
+        d = capi.describe_launch(True, rows, cols, F32)
+        assert d["pipelined"] == 1 and 2 * d["vecs_per_thread"] * (d["vector_bytes"] // 4) * 512 == cols
+        x, gamma, beta, dy, _ = U.make_inputs(11, rows, cols, F32)
+        f = O.norm_forward(x, gamma, beta)
+        dev = [t.cuda() for t in (dy, x, f["mean"], f["rstd"], gamma)]
+        dx = torch.zeros(rows, cols, device="cuda")
+        dgb = torch.empty(2 * cols, device="cuda")
+        ws = torch.empty(capi.backward_workspace_bytes(rows, cols, F32) // 4, device="cuda")
+        run = lambda: capi.norm_backward(capi.LAYERNORM, dev[0], dev[1], dev[2], dev[3], dev[4], None, dx, None, None,
+                                         dgb, ws)
+        hooks.fln_set_test_fault(1)
+        run()
+        torch.cuda.synchronize()
+        assert hooks.fln_device_status() == 1
+        hooks.fln_set_test_fault(0)
+        dx.zero_()
+        run()
+        torch.cuda.synchronize()
+        assert hooks.fln_device_status() == 0
+        want = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma)
+        torch.testing.assert_close(dx.cpu(), want["dx32"], rtol=1e-5, atol=1e-5)
+        U.assert_param_grads_close(dgb.cpu(), torch.cat([want["dgamma64"], want["dbeta64"]]), want["abs64"].reshape(-1), rows)
+    finally:
+        hooks.fln_set_path_override(0)
