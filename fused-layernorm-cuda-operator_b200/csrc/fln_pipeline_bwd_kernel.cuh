@@ -305,6 +305,15 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
           st_async_f32(theirs + n * 32 * 4, red[n], their_bar);
         }
       }
+      // the column sums do not need the row sums: they go here, under the exchange's latency
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+#pragma unroll
+        for (int e = 0; e < V2; ++e) {
+          acc_g[k][e] = f2fma(dyf[k][e], xh[k][e], acc_g[k][e]);
+          if (KIND == FLN_LAYERNORM) acc_b[k][e] = f2add(acc_b[k][e], dyf[k][e]);
+        }
+      }
       const bool theirs_landed = mbar_wait_bounded(&xbar[i & 1], (uint32_t)(i >> 1) & 1u, p.wait_ns);
       if (!__syncthreads_and(landed && theirs_landed ? 1 : 0)) {
         aborted = true;
@@ -357,12 +366,14 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
         }
       }
     }
+    if constexpr (!PAIR) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
+      for (int k = 0; k < K; ++k) {
 #pragma unroll
-      for (int e = 0; e < V2; ++e) {
-        acc_g[k][e] = f2fma(dyf[k][e], xh[k][e], acc_g[k][e]);
-        if (KIND == FLN_LAYERNORM) acc_b[k][e] = f2add(acc_b[k][e], dyf[k][e]);
+        for (int e = 0; e < V2; ++e) {
+          acc_g[k][e] = f2fma(dyf[k][e], xh[k][e], acc_g[k][e]);
+          if (KIND == FLN_LAYERNORM) acc_b[k][e] = f2add(acc_b[k][e], dyf[k][e]);
+        }
       }
     }
     if (++s == S) {
