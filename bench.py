@@ -439,6 +439,9 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist_
         dist = dist_
+        # NCCL writes its version banner (NCCL_DEBUG=VERSION and up) to stdout unless told
+        # otherwise; stdout of this script is the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     from fused_layernorm import _capi as capi
