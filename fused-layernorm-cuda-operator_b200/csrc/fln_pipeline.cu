@@ -223,7 +223,10 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // share of the rows when the first wave is done
   const int by_smem = (int)((227 * 1024) / P.smem);
   const int per_sm = by_smem < ctas_per_sm ? by_smem : ctas_per_sm;
-  const int64_t cap = (int64_t)usable_sms() * (per_sm < 1 ? 1 : per_sm);
+  // The SMs a caller asked to be left free (fln_set_sm_reserve) matter to the backward's static
+  // split only: a forward CTA that starts late behind somebody else's kernel just claims fewer
+  // tiles, so the forward fills every SM.
+  const int64_t cap = (int64_t)(backward ? usable_sms() : sm_count()) * (per_sm < 1 ? 1 : per_sm);
   P.grid = (int)(n_tiles < cap ? n_tiles : cap);
   return P;
 }

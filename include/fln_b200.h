@@ -345,10 +345,11 @@ void fln_set_plan_override(int vecs_per_thread, int threads_per_row);
  * backward launch.  Query fln_backward_workspace_bytes again after changing it. */
 void fln_set_path_override(int mode);
 
-/* Persistent kernels size their grids to fill every SM exactly and split the rows statically,
- * so a kernel of somebody else that holds an SM while one of them launches (a communication
- * kernel overlapped with the step, for instance) delays the CTAs that could not start, and
- * with them the whole launch.  This leaves `sms` SMs out of the persistent grids (default 0).
+/* The persistent backward kernels size their grids to fill every SM exactly and split the rows
+ * statically, so a kernel of somebody else that holds an SM while one of them launches (a
+ * communication kernel overlapped with the step, for instance) delays the CTAs that could not
+ * start, and with them the whole launch.  This leaves `sms` SMs out of those grids (default 0).
+ * The persistent forward hands its tiles out on demand and always uses every SM.
  * Query fln_backward_workspace_bytes again after changing it.  No counterpart in the reference. */
 void fln_set_sm_reserve(int sms);
 
