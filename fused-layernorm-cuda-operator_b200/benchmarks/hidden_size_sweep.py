@@ -56,8 +56,10 @@ def main():
     ap.add_argument("--skip-torch", action="store_true")
     ap.add_argument("--hidden", default=None, help="comma-separated hidden sizes instead of the built-in list")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--stages", type=int, default=0, help="fln_set_stage_override: stages per CTA of the pipelined kernels")
     args = ap.parse_args()
     capi.lib().fln_set_path_override(args.path_override)
+    capi.lib().fln_set_stage_override(args.stages)
     out = []
     for dn in args.dtypes.split(","):
         dt = getattr(torch, dn)
