@@ -439,10 +439,20 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist_
         dist = dist_
-        # NCCL writes its version banner (NCCL_DEBUG=VERSION and up) to stdout unless told
-        # otherwise; stdout of this script is the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL prints its version banner (NCCL_DEBUG=VERSION and up) on stdout when the first
+        # communicator comes up; stdout of this script is the one JSON line, so file descriptor 1
+        # points at stderr until that has happened
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     from fused_layernorm import _capi as capi
     from fused_layernorm.hostio import HostLayerNormFwdBwd
