@@ -384,6 +384,11 @@ struct FwdParams {
   unsigned long long wait_ns;
   int* status;
   const int* fault;
+  // fp8 forms of the pipelined forward only: e4m3 codes out (NULL: none), the scale they are
+  // made with, where max |y| of the call goes (NULL: nowhere)
+  void* q;
+  const float* scale_in;
+  float* amax;
 };
 
 struct BwdParams {
@@ -423,6 +428,9 @@ struct BwdParams {
 constexpr int FLN_PIPE_NOT_APPLICABLE = -1;
 int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p,
                         cudaStream_t st);
+// fp8 forms: e4m3 codes made with *p.scale_in into p.q when p.q is set, max |y| into *p.amax when
+// that is set (p.y is not written)
+int launch_fwd_pipeline_fp8(int kind, int io_dtype, const FwdParams& p, cudaStream_t st);
 // *reduced tells whether dgamma / dbeta / dgb_f32 were produced by the launch itself (fused
 // column reduce); otherwise the caller reduces p.partials.
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);

@@ -405,8 +405,10 @@ __global__ void __launch_bounds__(Fp8MaxThreads<K>::value) norm_quant_kernel(con
   }
 }
 
+// phase1_done: the pipelined forward has already written the sum, the statistics and amax of
+// the two-launch form; only the quantizing launch is left
 template <typename TI, int KIND>
-static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
+static int run_fp8(Fp8Params p, int qmode, cudaStream_t st, bool phase1_done) {
   constexpr int VFULL = 16 / sizeof(TI);
   Plan pl = make_plan(false, p.rows, p.cols, (int)sizeof(TI), true);
   if (pl.generic || pl.vec != VFULL) return FLN_ERR_UNSUPPORTED;
@@ -431,10 +433,11 @@ static int run_fp8(Fp8Params p, int qmode, cudaStream_t st) {
   const bool full = pl.tpr >= 32 && (int64_t)pl.K * pl.tpr == p.nv && p.rows % pl.rows_per_cta == 0;
   if (qmode == 3 && (p.cols % 32 != 0 || pl.tpr < 32 / VFULL)) return FLN_ERR_UNSUPPORTED;
   if (qmode == 4 && (p.cols % 16 != 0 || pl.tpr < 16 / VFULL)) return FLN_ERR_UNSUPPORTED;
-  if (p.amax != nullptr && cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+  if (!phase1_done && p.amax != nullptr && cudaMemsetAsync(p.amax, 0, sizeof(float), st) != cudaSuccess)
+    return FLN_ERR_LAUNCH;
 #define FLN_FP8_LAUNCH(KK, FF)                                                                  \
   if (qmode == 0) {                                                                             \
-    norm_amax_kernel<TI, VFULL, KK, KIND, FF, 0><<<grid, pl.threads, 0, st>>>(p);               \
+    if (!phase1_done) norm_amax_kernel<TI, VFULL, KK, KIND, FF, 0><<<grid, pl.threads, 0, st>>>(p); \
     norm_quant_kernel<TI, VFULL, KK, KIND, FF><<<grid, pl.threads, 0, st>>>(p);                 \
   } else if (qmode == 1) {                                                                      \
     norm_amax_kernel<TI, VFULL, KK, KIND, FF, 1><<<grid, pl.threads, 0, st>>>(p);               \
@@ -523,8 +526,45 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
   p.tpr = 0;
   p.log2_tpr = 0;
   p.eps = eps;
-#define FLN_RUN(T) \
-  (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, qmode, st) : run_fp8<T, FLN_RMSNORM>(p, qmode, st))
+  // Large 16-bit problems with a per-tensor scale: the normalization itself runs in the
+  // persistent pipelined forward -- all of the delayed-scale form, phase 1 (sum, statistics,
+  // amax) of the two-launch form.
+  bool phase1_done = false;
+  if ((qmode == 0 || qmode == 1) && io_dtype != FLN_F32) {
+    FwdParams f;
+    f.x = x;
+    f.res = residual;
+    f.gamma = gamma;
+    f.beta = beta;
+    f.y = nullptr;
+    f.sum_out = sum_out;
+    f.mean = mean;
+    f.rstd = rstd;
+    f.rows = rows;
+    f.cols = (int)cols;
+    f.nv = 0;
+    f.tpr = 0;
+    f.log2_tpr = 0;
+    f.eps = eps;
+    f.sched = nullptr;
+    f.wait_ns = 0;
+    f.status = nullptr;
+    f.fault = nullptr;
+    f.q = qmode == 1 ? q : nullptr;
+    f.scale_in = scale_in;
+    f.amax = amax;
+    if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+    const int rc = launch_fwd_pipeline_fp8(kind, io_dtype, f, st);
+    if (rc == FLN_OK) {
+      if (qmode == 1) return FLN_OK;
+      phase1_done = true;
+    } else if (rc != FLN_PIPE_NOT_APPLICABLE) {
+      return rc;
+    }
+  }
+#define FLN_RUN(T)                                                                  \
+  (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, qmode, st, phase1_done)     \
+                         : run_fp8<T, FLN_RMSNORM>(p, qmode, st, phase1_done))
   if (io_dtype == FLN_F32) return FLN_RUN(float);
   if (io_dtype == FLN_BF16) return FLN_RUN(__nv_bfloat16);
   return FLN_RUN(__half);

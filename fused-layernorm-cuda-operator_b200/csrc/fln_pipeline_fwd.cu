@@ -1,313 +1,7 @@
-// Pipelined forward: the kernel and its dispatch.  See fln_pipeline.cuh for the ring and the
-// scheduling of tiles.
-#include "fln_pipeline.cuh"
+// Pipelined forward: dispatch and entry point.  The kernel is in fln_pipeline_fwd_kernel.cuh.
+#include "fln_pipeline_fwd_kernel.cuh"
 
 namespace fln {
-
-// ----------------------------------------------------------------------------------------
-// forward
-//
-// Per pair of elements: one shift and one mask (widen), then on the register pair: shift by c
-// and add (row sum), centre, one fma (sum of squares), one multiply and one fma (normalize +
-// affine), one paired convert.  Statistics are the two-pass form on the row shifted by its
-// first element, each pass reduced by a warp butterfly plus one shared-memory hop.
-//
-// Tiles: every CTA starts with tiles b, b + grid, ..., b + (S - 1) grid (no round trip before
-// its first copies leave), then claims further tiles from the launch's counter, one claim
-// ahead of need so that the atomic's latency never sits in front of a refill.  The thread
-// that refills a stage notes the stage's tile in shared memory in front of arming the
-// barrier; a stage whose claim came back beyond the last tile is armed without a copy and
-// marked empty, and a CTA that meets an empty stage is done (claims only grow).
-// ----------------------------------------------------------------------------------------
-// MODE 0: general (bounds-checked); 1: FULL (no predication in the loop).
-// MODE 4: FULL with gamma / beta parked in shared memory (in the I/O type) instead of in
-// registers as floats, for plans that give a thread more than 32 elements (row lengths
-// 5 * 2^a in 16-bit types: 40 elements per thread keep the 16-byte vectors and move more
-// bytes per barrier than 20 elements in 8-byte vectors)
-// MODE 5: rows whole, every vector whole except the last of a thread's K (rows that fit no
-// exact plan, 1600 columns: K = 7, lanes beyond the row idle in the seventh vector only); the
-// row length comes from the launch parameters, the split from LT.
-// LT >= 0: the geometry is known at compile time -- a CTA of 256 threads (512 for LT = 9), 2^LT threads per row,
-// rows of exactly K * VEC * 2^LT elements (FULL).  Row length, byte offsets of a thread's
-// vectors and the shape of the reductions then fold into immediates: the bf16 forward at
-// 16384 x 8192 executes 8.4 instead of 11.3 instructions per element and takes 83 instead of
-// 101 us.  LT < 0 takes all of it from the launch parameters.
-template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1>
-__global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
-  constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
-  constexpr int V2 = VEC / 2;
-  constexpr bool FULL = MODE >= 1;
-  constexpr bool PSM = MODE == 4;
-  constexpr bool TAIL = MODE == 5;
-  constexpr bool CT = LT >= 0;
-  constexpr int LTC = CT ? LT : 0;
-  constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
-  static_assert(!CT || MODE == 1 || MODE == 4 || MODE == 5, "compile-time geometry is for the FULL kernels");
-  static_assert(!TAIL || CT, "the ragged-last-vector kernel has its split at compile time");
-// vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
-#define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
-  const int tpr = CT ? (1 << LTC) : g.tpr;
-  const int log2_tpr = CT ? LTC : g.log2_tpr;
-  const int R = CT ? (NT >> LTC) : g.R;
-  const int cols = (CT && !TAIL) ? ((K * VEC) << LTC) : p.cols;
-  const uint32_t row_bytes = (CT && !TAIL) ? (uint32_t)((K * VB) << LTC) : g.row_bytes;
-  const uint32_t second_off = CT ? row_bytes * (uint32_t)R : g.second_off;
-  extern __shared__ __align__(128) unsigned char smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  unsigned int* tile_of = reinterpret_cast<unsigned int*>(smem + 128);
-  float* s_red = reinterpret_cast<float*>(smem + 256);  // 2 x 64 + 2 x 32 floats
-  unsigned char* stages = smem + kSmemHeader;
-
-  const int tid = threadIdx.x;
-  const int lane_r = tid & (tpr - 1);
-  const int r_in = tid >> log2_tpr;
-  const int S = g.S;
-  const unsigned int n_tiles = (unsigned int)((p.rows + R - 1) / R);
-  const bool has_res = p.res != nullptr;
-  const float inv_n = 1.0f / (float)cols;
-  const float eps = p.eps;
-  unsigned int* sched = p.sched;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
-    mbar_init_fence();
-  }
-  __syncthreads();
-
-  // ---- producer (thread 0)
-  const unsigned int dyn_base = gridDim.x * (unsigned int)S;
-  unsigned int next_t = kNoTile;  // the tile claimed ahead
-  auto fill = [&](unsigned int t, int s, bool skip_copy) {
-    if (t < n_tiles) {
-      const int64_t row0 = (int64_t)t * R;
-      const int64_t left = p.rows - row0;
-      const uint32_t bytes = (uint32_t)(left < R ? left : R) * row_bytes;
-      unsigned char* dst = stages + (size_t)s * g.stage_stride;
-      tile_of[s] = t;
-      mbar_expect_tx(&full[s], has_res ? 2 * bytes : bytes);
-      if (!skip_copy) {
-        bulk_g2s(dst, reinterpret_cast<const TI*>(p.x) + row0 * cols, bytes, &full[s]);
-        if (has_res)
-          bulk_g2s(dst + second_off, reinterpret_cast<const TI*>(p.res) + row0 * cols, bytes, &full[s]);
-      }
-    } else {
-      tile_of[s] = kNoTile;
-      mbar_arrive(&full[s]);
-    }
-  };
-  if (tid == 0) {
-    // test hook (fln_set_test_fault bit 0): CTA 0 arms its first stage without the copy
-    const bool fault = blockIdx.x == 0 && (*p.fault & 1) != 0;
-    for (int s = 0; s < S; ++s) fill(blockIdx.x + (unsigned int)s * gridDim.x, s, fault && s == 0);
-    next_t = dyn_base + atomicAdd(sched, 1u);
-  }
-
-  float2 gam[PSM ? 1 : K][V2], bet[PSM ? 1 : K][V2];
-  bool vok[K];  // does vector k of this thread exist in the row
-  unsigned char* s_gamma = stages + (size_t)S * g.stage_stride;  // PSM: [cols] gamma, then [cols] beta
-  unsigned char* s_beta = s_gamma + row_bytes;
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const int iv = lane_r + k * tpr;
-    vok[k] = FLN_WHOLE(k) ? true : iv < p.nv;
-    if constexpr (PSM) {
-      if (r_in == 0) {
-        Pack<TI, VEC> one, zero;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          one.e[e] = Cvt<TI>::from_f(1.f);
-          zero.e[e] = Cvt<TI>::from_f(0.f);
-        }
-        *reinterpret_cast<Pack<TI, VEC>*>(s_gamma + (size_t)iv * VB) =
-            p.gamma != nullptr ? ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC) : one;
-        *reinterpret_cast<Pack<TI, VEC>*>(s_beta + (size_t)iv * VB) =
-            p.beta != nullptr ? ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC) : zero;
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < V2; ++e) {
-        gam[k][e] = f2(1.f);
-        bet[k][e] = f2(0.f);
-      }
-      if (vok[k]) {
-        if (p.gamma != nullptr)
-          unpack2<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + (int64_t)iv * VEC), gam[k]);
-        if (p.beta != nullptr)
-          unpack2<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC), bet[k]);
-      }
-    }
-  }
-  if constexpr (PSM) __syncthreads();
-
-  int s = 0;
-  uint32_t phase = 0;
-  bool aborted = false;
-  const uint32_t my_off = (uint32_t)r_in * row_bytes + (uint32_t)lane_r * (uint32_t)VB;
-  const uint32_t k_off = (uint32_t)tpr * (uint32_t)VB;
-  for (int i = 0;; ++i) {
-    const bool landed = mbar_wait_bounded(&full[s], phase, p.wait_ns);
-    // written by the producer before the last CTA barrier at the latest, so every thread reads
-    // the same value here whether or not its wait succeeded
-    const unsigned int tile = tile_of[s];
-    if (tile == kNoTile) break;
-    const int64_t row = (int64_t)tile * R + r_in;
-    const bool row_ok = FULL ? true : row < p.rows;
-    const unsigned char* st = stages + (size_t)s * g.stage_stride + my_off;
-    float* redA = s_red + (i & 1) * 64;
-    float* redB = s_red + 128 + (i & 1) * 32;
-
-    float2 f[K][V2];
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      if (FLN_WHOLE(k) || (row_ok && vok[k])) {
-        unpack2<TI, VEC>(stage_vec<TI, VEC>(st + k * k_off), f[k]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < V2; ++e) f[k][e] = f2(0.f);
-      }
-    }
-    if (has_res) {
-      TI* __restrict__ sr = reinterpret_cast<TI*>(p.sum_out) + row * (int64_t)cols + (int64_t)lane_r * VEC;
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        if (FLN_WHOLE(k) || (row_ok && vok[k])) {
-          float2 r[V2];
-          unpack2<TI, VEC>(stage_vec<TI, VEC>(st + second_off + k * k_off), r);
-#pragma unroll
-          for (int e = 0; e < V2; ++e) f[k][e] = f2add(f[k][e], r[e]);
-          // the sum is rounded to the I/O type first: that value is normalized and stored
-          Pack<TI, VEC> q;
-          pack2<TI, VEC>(f[k], q);
-          st_stream<TI, VEC>(sr + (int64_t)k * tpr * VEC, q);
-          unpack2<TI, VEC>(q, f[k]);
-        }
-      }
-    }
-
-    float mean = 0.f;
-    if (KIND == FLN_LAYERNORM) {
-      // shift by element 0 of the row (a broadcast read of the stage): a constant row then
-      // sums to exactly zero whatever its magnitude, and |mean| >> std costs no accuracy
-      const unsigned char* st0 = st - (size_t)lane_r * VB;
-      float c = Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0));
-      if (has_res)
-        c = Cvt<TI>::to_f(Cvt<TI>::from_f(c + Cvt<TI>::to_f(*reinterpret_cast<const TI*>(st0 + second_off))));
-      const float2 nc = f2(-c);
-      float2 a01 = f2(0.f), a23 = f2(0.f);  // four chains: the adds are latency-bound
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        if (FLN_WHOLE(k) || vok[k]) {  // padding vectors stay zero
-#pragma unroll
-          for (int e = 0; e < V2; e += 2) {
-            f[k][e] = f2add(f[k][e], nc);
-            f[k][e + 1] = f2add(f[k][e + 1], nc);
-            a01 = f2add(a01, f[k][e]);
-            a23 = f2add(a23, f[k][e + 1]);
-          }
-        }
-      }
-      float ar[1] = {(a01.x + a01.y) + (a23.x + a23.y)};
-      rowsum_warp<1>(ar, tpr, redA);
-      // The first barrier of a tile also proves that every thread has pulled its part of
-      // stage s into registers, so the producer may refill the stage right after it.
-      if (!__syncthreads_and(landed ? 1 : 0)) {
-        aborted = true;
-        break;
-      }
-      if (tid == 0) {
-        fill(next_t, s, false);
-        if (next_t < n_tiles) next_t = dyn_base + atomicAdd(sched, 1u);
-      }
-      rowsum_cta<1>(ar, tpr, redA);
-      const float ms = ar[0] * inv_n;  // mean of the shifted row
-      mean = c + ms;
-      const float2 nms = f2(-ms);
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        if (FLN_WHOLE(k) || vok[k]) {
-#pragma unroll
-          for (int e = 0; e < V2; ++e) f[k][e] = f2add(f[k][e], nms);
-        }
-      }
-    }
-    float2 q01 = f2(0.f), q23 = f2(0.f);
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-#pragma unroll
-      for (int e = 0; e < V2; e += 2) {
-        q01 = f2fma(f[k][e], f[k][e], q01);
-        q23 = f2fma(f[k][e + 1], f[k][e + 1], q23);
-      }
-    }
-    float q[1] = {(q01.x + q01.y) + (q23.x + q23.y)};
-    rowsum_warp<1>(q, tpr, redB);
-    if (KIND == FLN_LAYERNORM) {
-      __syncthreads();
-    } else {
-      if (!__syncthreads_and(landed ? 1 : 0)) {
-        aborted = true;
-        break;
-      }
-      if (tid == 0) {
-        fill(next_t, s, false);
-        if (next_t < n_tiles) next_t = dyn_base + atomicAdd(sched, 1u);
-      }
-    }
-    rowsum_cta<1>(q, tpr, redB);
-    const float rstd = rsqrtf(fmaf(q[0], inv_n, eps));
-
-    if (row_ok && lane_r == 0) {
-      if (KIND == FLN_LAYERNORM && p.mean != nullptr) p.mean[row] = mean;
-      if (p.rstd != nullptr) p.rstd[row] = rstd;
-    }
-    TO* __restrict__ yr = reinterpret_cast<TO*>(p.y) + row * (int64_t)cols + (int64_t)lane_r * VEC;
-    const float2 r2 = f2(rstd);
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      if (FLN_WHOLE(k) || (row_ok && vok[k])) {
-        float2 o[V2];
-        if constexpr (PSM) {
-          float2 gw[V2], bw[V2];
-          const size_t po = (size_t)(lane_r + k * tpr) * VB;
-          unpack2<TI, VEC>(stage_vec<TI, VEC>(s_gamma + po), gw);
-          unpack2<TI, VEC>(stage_vec<TI, VEC>(s_beta + po), bw);
-#pragma unroll
-          for (int e = 0; e < V2; ++e) o[e] = f2fma(f2mul(f[k][e], r2), gw[e], bw[e]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < V2; ++e) o[e] = f2fma(f2mul(f[k][e], r2), gam[k][e], bet[k][e]);
-        }
-        if (ACT != FLN_ACT_NONE) {
-#pragma unroll
-          for (int e = 0; e < V2; ++e) o[e] = make_float2(apply_act<ACT>(o[e].x), apply_act<ACT>(o[e].y));
-        }
-        Pack<TO, VEC> out;
-        pack2<TO, VEC>(o, out);
-        st_stream<TO, VEC>(yr + (int64_t)k * tpr * VEC, out);
-      }
-    }
-    if (++s == S) {
-      s = 0;
-      phase ^= 1u;
-    }
-  }
-
-  // ---- exit: every CTA counts itself out; the last one puts the launch's counter pair back
-  // to zero and checks that the claims add up (every tile beyond the static ones claimed once,
-  // and one claim beyond the end per CTA)
-  if (tid == 0) {
-    if (aborted) pipeline_abort(p.status, full, S, s, phase, S, p.wait_ns);  // every stage of this ring is always armed
-    __threadfence();
-    const unsigned int done = atomicAdd(sched + 1, 1u);
-    if (done == gridDim.x - 1) {
-      const unsigned int claims = atomicExch(sched, 0u);
-      const unsigned int dyn_tiles = n_tiles > dyn_base ? n_tiles - dyn_base : 0u;
-      if (claims != dyn_tiles + gridDim.x && (*p.status & 1) == 0) atomicOr(p.status, 4);
-      atomicExch(sched + 1, 0u);
-    }
-  }
-}
-#undef FLN_WHOLE
 
 // one branch-free instantiation with an odd K and / or short vectors; combinations that make no
 // sense for the type (too many elements per thread, vectors shorter than four elements) are
@@ -434,6 +128,16 @@ static int fwd_pipe_typed(int kind, int act, const FwdParams& p, const PipePlan&
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
+bool fwd_pipe_prepare(FwdParams* p) {
+  DeviceWords w;
+  if (!device_words(&w)) return false;
+  p->sched = w.sched + 2 * next_sched_slot();
+  p->wait_ns = wait_limit_ns();
+  p->status = w.status;
+  p->fault = w.fault;
+  return true;
+}
+
 int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p0,
                         cudaStream_t st) {
   const int es = io_dtype == FLN_F32 ? 4 : 2;
@@ -459,12 +163,7 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
   }
   FwdParams p = p0;
   p.nv = p.cols / (P.vb / es);
-  DeviceWords w;
-  if (!device_words(&w)) return FLN_ERR_LAUNCH;
-  p.sched = w.sched + 2 * next_sched_slot();
-  p.wait_ns = wait_limit_ns();
-  p.status = w.status;
-  p.fault = w.fault;
+  if (!fwd_pipe_prepare(&p)) return FLN_ERR_LAUNCH;
   if (io_dtype == FLN_F32 && out_dtype == FLN_F32) return fwd_pipe_typed<float, float>(kind, act, p, P, st);
   if (io_dtype == FLN_F32 && out_dtype == FLN_BF16) return fwd_pipe_typed<float, __nv_bfloat16>(kind, act, p, P, st);
   if (io_dtype == FLN_BF16) return fwd_pipe_typed<__nv_bfloat16, __nv_bfloat16>(kind, act, p, P, st);

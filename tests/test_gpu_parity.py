@@ -317,6 +317,56 @@ def test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residu
     torch.testing.assert_close(rstd.cpu(), want["rstd"], rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("rmsnorm", False), ("layernorm", True)])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("shape", [(1024, 8192), (2048, 1024), (768, 3072), (512, 16384), (1200, 768)])
+def test_fp8_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
+    """Large 16-bit problems with a per-tensor scale are normalized by the persistent pipelined
+    forward (forced here for medium sizes): the two-launch form (amax in the kernel) and the
+    delayed-scale form, 4 and 3 vectors per thread, against the checker; the statistics too."""
+    path_override(2)
+    rows, cols = shape
+    x, gamma, beta, _, res = U.make_inputs(20250 + cols, rows, cols, dtype, residual=residual, outliers=True)
+    if kind == "rmsnorm":
+        beta = None
+    want = O.norm_forward(x, gamma, beta, res, kind, 1e-6)
+    y32 = want["y32"]
+
+    def check_codes(q, wq):
+        d = O.fp8_code_distance(q.check().cpu(), wq)
+        assert int(d.max()) <= 1
+        assert int((d > 0).sum()) <= max(1, int(1e-4 * d.numel()))
+
+    for form in ("two_launch", "delayed"):
+        q = U.Guarded((rows, cols), torch.uint8)
+        s = U.Guarded((rows, cols), dtype) if residual else None
+        mean = U.Guarded((rows,), torch.float32) if kind == "layernorm" else None
+        rstd = U.Guarded((rows,), torch.float32)
+        amax = torch.full((1,), -1.0, device="cuda")
+        if form == "two_launch":
+            scale = torch.full((1,), -1.0, device="cuda")
+            capi.norm_forward_fp8(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t,
+                                  s.t if s else None, mean.t if mean else None, rstd.t, amax, scale, 1e-6)
+            torch.cuda.synchronize()
+            wq, wamax, wscale = O.quant_fp8(y32)
+            torch.testing.assert_close(scale.cpu(), wscale, rtol=1e-5, atol=0)
+        else:
+            stale = torch.tensor([1.5 * 448.0 / float(y32.abs().max())])
+            capi.norm_forward_fp8_delayed(U.KINDS[kind], U.dev(x), U.dev(res), U.dev(gamma), U.dev(beta), q.t,
+                                          s.t if s else None, mean.t if mean else None, rstd.t, stale.cuda(), amax,
+                                          1e-6)
+            torch.cuda.synchronize()
+            wq, wamax = O.quant_fp8_delayed(y32, stale)
+        torch.testing.assert_close(amax.cpu(), wamax, rtol=1e-5, atol=0)
+        check_codes(q, wq)
+        torch.testing.assert_close(rstd.check().cpu(), want["rstd"], rtol=1e-5, atol=1e-6)
+        if kind == "layernorm":
+            torch.testing.assert_close(mean.check().cpu(), want["mean"], rtol=1e-5, atol=1e-5)
+        if residual:
+            assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
+    assert capi.lib().fln_device_status() == 0
+
+
 @pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
 @pytest.mark.parametrize("dtype", [BF16, F16, F32])
 @pytest.mark.parametrize("shape", [(64, 8192), (257, 1024), (5, 4096), (33, 96)])
