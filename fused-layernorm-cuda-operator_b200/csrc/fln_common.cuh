@@ -389,6 +389,8 @@ struct FwdParams {
   void* q;
   const float* scale_in;
   float* amax;
+  unsigned char* block_scale;  // MXFP8: [rows, cols / 32] E8M0 bytes; NVFP4: [rows, cols / 16] e4m3 bytes
+  float* row_scale;            // per-row scales: [rows]
 };
 
 struct BwdParams {
@@ -430,7 +432,9 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
                         cudaStream_t st);
 // fp8 forms: e4m3 codes made with *p.scale_in into p.q when p.q is set, max |y| into *p.amax when
 // that is set (p.y is not written)
-int launch_fwd_pipeline_fp8(int kind, int io_dtype, const FwdParams& p, cudaStream_t st);
+// qm 1: per-tensor scale as above; 2: one scale per row (p.row_scale); 3: MXFP8; 4: NVFP4-style
+// (both with p.block_scale)
+int launch_fwd_pipeline_fp8(int kind, int io_dtype, int qm, const FwdParams& p, cudaStream_t st);
 // *reduced tells whether dgamma / dbeta / dgb_f32 were produced by the launch itself (fused
 // column reduce); otherwise the caller reduces p.partials.
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);

@@ -389,6 +389,8 @@ extern "C" int fln_norm_forward(int kind, const void* x, const void* residual, c
   p.q = nullptr;
   p.scale_in = nullptr;
   p.amax = nullptr;
+  p.block_scale = nullptr;
+  p.row_scale = nullptr;
   const bool aligned = is_aligned16(x) && is_aligned16(y) && is_aligned16(residual) &&
                        is_aligned16(sum_out) && is_aligned16(gamma) && is_aligned16(beta);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

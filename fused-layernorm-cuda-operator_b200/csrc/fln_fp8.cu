@@ -526,11 +526,11 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
   p.tpr = 0;
   p.log2_tpr = 0;
   p.eps = eps;
-  // Large 16-bit problems with a per-tensor scale: the normalization itself runs in the
-  // persistent pipelined forward -- all of the delayed-scale form, phase 1 (sum, statistics,
-  // amax) of the two-launch form.
+  // Large 16-bit problems: the normalization itself runs in the persistent pipelined forward --
+  // all of the delayed-scale, per-row, MXFP8 and NVFP4 forms, phase 1 (sum, statistics, amax) of
+  // the two-launch form.
   bool phase1_done = false;
-  if ((qmode == 0 || qmode == 1) && io_dtype != FLN_F32) {
+  if (io_dtype != FLN_F32) {
     FwdParams f;
     f.x = x;
     f.res = residual;
@@ -550,13 +550,15 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
     f.wait_ns = 0;
     f.status = nullptr;
     f.fault = nullptr;
-    f.q = qmode == 1 ? q : nullptr;
+    f.q = qmode == 0 ? nullptr : q;
     f.scale_in = scale_in;
     f.amax = amax;
+    f.block_scale = block_scale;
+    f.row_scale = row_scale;
     if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
-    const int rc = launch_fwd_pipeline_fp8(kind, io_dtype, f, st);
+    const int rc = launch_fwd_pipeline_fp8(kind, io_dtype, qmode == 0 ? 1 : qmode, f, st);
     if (rc == FLN_OK) {
-      if (qmode == 1) return FLN_OK;
+      if (qmode != 0) return FLN_OK;
       phase1_done = true;
     } else if (rc != FLN_PIPE_NOT_APPLICABLE) {
       return rc;

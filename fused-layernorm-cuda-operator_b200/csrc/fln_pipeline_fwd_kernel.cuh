@@ -2,6 +2,7 @@
 // Instantiated in fln_pipeline_fwd.cu (the forward entry point) and fln_pipeline_fwd_fp8.cu (the
 // fp8 outputs).
 #pragma once
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "fln_pipeline.cuh"
@@ -36,15 +37,25 @@ namespace fln {
 // vectors and the shape of the reductions then fold into immediates: the bf16 forward at
 // 16384 x 8192 executes 8.4 instead of 11.3 instructions per element and takes 83 instead of
 // 101 us.  LT < 0 takes all of it from the launch parameters.
-// Q8: the fp8 forms.  y is not stored in TO; instead max |y| of the launch goes to *p.amax (if
-// set) and, if p.q is set, y * *p.scale_in goes out as saturating e4m3 codes, two per conversion.
-template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1, bool Q8 = false>
+// QM > 0: the quantized outputs.  y is not stored in TO; max |y| of the launch goes to *p.amax
+// (if set) and
+//   QM 1: if p.q is set, y * *p.scale_in goes out as saturating e4m3 codes, two per conversion;
+//   QM 2: e4m3 codes with one scale per row, 448 / max |y| of the row (written to p.row_scale);
+//   QM 3: MXFP8 -- e4m3 codes with one power-of-two scale (an E8M0 byte in p.block_scale) per 32
+//         consecutive elements, 2^(floor(log2(block max)) - 8); the 32 elements sit in four
+//         neighbouring lanes;
+//   QM 4: NVFP4-style -- e2m1 codes, two per byte, one e4m3 scale per 16 elements (two
+//         neighbouring lanes), b = e4m3(block max * S / 6), q = e2m1(y * S / float(b)), S =
+//         *p.scale_in.
+template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1, int QM = 0>
 __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr int V2 = VEC / 2;
   constexpr bool FULL = MODE >= 1;
   constexpr bool PSM = MODE == 4;
   constexpr bool TAIL = MODE == 5;
+  constexpr bool Q8 = QM > 0;
+  static_assert(QM == 0 || (VEC == 8 && MODE == 1), "quantized outputs: 16-bit input, 16-byte vectors, exact rows");
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
@@ -147,9 +158,10 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
 
   float amax = 0.f;
   float2 qs2 = f2(1.f);
-  if constexpr (Q8) {
+  if constexpr (QM == 1) {
     if (p.q != nullptr) qs2 = f2(__ldg(p.scale_in));
   }
+  if constexpr (QM == 4) qs2 = f2(__ldg(p.scale_in));
   int s = 0;
   uint32_t phase = 0;
   bool aborted = false;
@@ -273,6 +285,33 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     }
     TO* __restrict__ yr = reinterpret_cast<TO*>(p.y) + row * (int64_t)cols + (int64_t)lane_r * VEC;
     const float2 r2 = f2(rstd);
+    if constexpr (QM == 2) {
+      // the row's maximum first (y is cheap to form twice: two operations per pair), then its scale
+      float rm = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+#pragma unroll
+        for (int e = 0; e < V2; ++e) {
+          const float2 o = f2fma(f2mul(f[k][e], r2), gam[k][e], bet[k][e]);
+          rm = fmaxf(rm, fmaxf(fabsf(o.x), fabsf(o.y)));
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, off));
+      if (tpr > 32) {
+        float* s_rmax = reinterpret_cast<float*>(smem + 1024) + (i & 1) * 32;
+        const int warp = tid >> 5, wpr = tpr >> 5;
+        if ((tid & 31) == 0) s_rmax[warp] = rm;
+        __syncthreads();
+        const int gbase = warp & ~(wpr - 1);
+        rm = s_rmax[gbase];
+        for (int j = 1; j < wpr; ++j) rm = fmaxf(rm, s_rmax[gbase + j]);
+      }
+      amax = fmaxf(amax, rm);
+      const float rs = rm > 0.f ? 448.0f / rm : 1.0f;
+      qs2 = f2(rs);
+      if (lane_r == 0) p.row_scale[row] = rs;
+    }
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (FLN_WHOLE(k) || (row_ok && vok[k])) {
@@ -295,15 +334,54 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
         if constexpr (Q8) {
 #pragma unroll
           for (int e = 0; e < V2; ++e) amax = fmaxf(amax, fmaxf(fabsf(o[e].x), fabsf(o[e].y)));  // fmaxf drops NaN
-          if (p.q != nullptr) {
-            Pack<unsigned char, VEC> out;
-            unsigned short* w = reinterpret_cast<unsigned short*>(&out);
+          if constexpr (QM == 1 || QM == 2) {
+            if (QM == 2 || p.q != nullptr) {
+              Pack<unsigned char, VEC> out;
+              unsigned short* w = reinterpret_cast<unsigned short*>(&out);
 #pragma unroll
-            for (int e = 0; e < V2; ++e)
-              w[e] = __nv_cvt_float2_to_fp8x2(f2mul(o[e], qs2), __NV_SATFINITE, __NV_E4M3);
-            st_stream<unsigned char, VEC>(reinterpret_cast<unsigned char*>(p.q) + row * (int64_t)cols +
-                                              (int64_t)(lane_r + k * tpr) * VEC,
-                                          out);
+              for (int e = 0; e < V2; ++e)
+                w[e] = __nv_cvt_float2_to_fp8x2(f2mul(o[e], qs2), __NV_SATFINITE, __NV_E4M3);
+              st_stream<unsigned char, VEC>(reinterpret_cast<unsigned char*>(p.q) + row * (int64_t)cols +
+                                                (int64_t)(lane_r + k * tpr) * VEC,
+                                            out);
+            }
+          } else {
+            // block-scaled: the maximum of this thread's vector, then of the block's lanes
+            const int iv = lane_r + k * tpr;
+            float bm = 0.f;
+#pragma unroll
+            for (int e = 0; e < V2; ++e) bm = fmaxf(bm, fmaxf(fabsf(o[e].x), fabsf(o[e].y)));
+            constexpr int G = (QM == 3 ? 32 : 16) / VEC;
+#pragma unroll
+            for (int off = 1; off < G; off <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, off));
+            if constexpr (QM == 3) {
+              const unsigned int ef = (__float_as_uint(bm) >> 23) & 0xffu;  // biased exponent of the block maximum
+              const unsigned int e8 = ef > 8u ? ef - 8u : 0u;               // the scale is 2^(e8 - 127)
+              const float2 inv = f2(__uint_as_float((254u - e8) << 23));    // 2^(127 - e8), exact
+              Pack<unsigned char, VEC> out;
+              unsigned short* w = reinterpret_cast<unsigned short*>(&out);
+#pragma unroll
+              for (int e = 0; e < V2; ++e)
+                w[e] = __nv_cvt_float2_to_fp8x2(f2mul(o[e], inv), __NV_SATFINITE, __NV_E4M3);
+              st_stream<unsigned char, VEC>(reinterpret_cast<unsigned char*>(p.q) + row * (int64_t)cols +
+                                                (int64_t)iv * VEC,
+                                            out);
+              if ((lane_r & (G - 1)) == 0) p.block_scale[row * (int64_t)(cols / 32) + iv / G] = (unsigned char)e8;
+            } else {
+              const float S = qs2.x;
+              const unsigned char sb = (unsigned char)__nv_cvt_float_to_fp8(__fmul_rn(__fmul_rn(bm, S), 1.0f / 6.0f),
+                                                                            __NV_SATFINITE, __NV_E4M3);
+              const float fb = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
+              const float invs = fb > 0.f ? __fdiv_rn(S, fb) : 0.f;
+              Pack<unsigned char, VEC / 2> out;
+#pragma unroll
+              for (int e = 0; e < V2; ++e)
+                out.e[e] = (unsigned char)__nv_cvt_float2_to_fp4x2(
+                    make_float2(__fmul_rn(o[e].x, invs), __fmul_rn(o[e].y, invs)), __NV_E2M1, cudaRoundNearest);
+              st_stream<unsigned char, VEC / 2>(
+                  reinterpret_cast<unsigned char*>(p.q) + ((row * (int64_t)cols) >> 1) + (int64_t)iv * (VEC / 2), out);
+              if ((lane_r & (G - 1)) == 0) p.block_scale[row * (int64_t)(cols / 16) + iv / G] = sb;
+            }
           }
         } else {
           Pack<TO, VEC> out;

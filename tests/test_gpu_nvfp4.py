@@ -61,6 +61,20 @@ def test_nvfp4_block_scaled_output(shape, dtype, kind, residual):
         assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
 
 
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024)])
+@pytest.mark.parametrize("dtype", [BF16, torch.float16])
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
+def test_nvfp4_through_the_pipelined_forward(shape, dtype, kind, residual):
+    """The same checks with the persistent pipelined forward doing the work (forced for these
+    medium sizes; large 16-bit problems take it by themselves)."""
+    capi.lib().fln_set_path_override(2)
+    try:
+        test_nvfp4_block_scaled_output(shape, dtype, kind, residual)
+        assert capi.lib().fln_device_status() == 0
+    finally:
+        capi.lib().fln_set_path_override(0)
+
+
 def test_nvfp4_python_api_and_errors():
     import fused_layernorm as fl
     x = torch.randn(2, 8, 256, device="cuda", dtype=BF16)

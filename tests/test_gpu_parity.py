@@ -402,6 +402,26 @@ def test_mxfp8_block_scaled_output(shape, dtype, kind, residual):
         assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
 
 
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", True)])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024), (512, 16384)])
+def test_fp8_per_row_scales_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
+    path_override(2)
+    test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residual)
+    assert capi.lib().fln_device_status() == 0
+
+
+@pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024)])
+def test_mxfp8_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
+    """The same checks with the persistent pipelined forward doing the work (forced for these
+    medium sizes; large 16-bit problems take it by themselves)."""
+    path_override(2)
+    test_mxfp8_block_scaled_output(shape, dtype, kind, residual)
+    assert capi.lib().fln_device_status() == 0
+
+
 def test_fp8_rejects_ragged_rows():
     x = torch.randn(4, 1023, device="cuda", dtype=BF16)
     q = torch.empty(4, 1023, dtype=torch.uint8, device="cuda")
