@@ -391,6 +391,11 @@ struct FwdParams {
   float* amax;
   unsigned char* block_scale;  // MXFP8: [rows, cols / 32] E8M0 bytes; NVFP4: [rows, cols / 16] e4m3 bytes
   float* row_scale;            // per-row scales: [rows]
+  // dropout form of the pipelined forward only
+  unsigned char* keep_bits;  // one byte per 8 elements, or NULL
+  unsigned long long drop_seed, drop_offset;
+  unsigned int drop_threshold;  // 0: keep everything
+  float drop_scale;
 };
 
 struct BwdParams {
@@ -435,6 +440,8 @@ int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const Fw
 // qm 1: per-tensor scale as above; 2: one scale per row (p.row_scale); 3: MXFP8; 4: NVFP4-style
 // (both with p.block_scale)
 int launch_fwd_pipeline_fp8(int kind, int io_dtype, int qm, const FwdParams& p, cudaStream_t st);
+// dropout -> residual add -> norm (p.keep_bits, p.drop_*); p.sum_out may be NULL
+int launch_fwd_pipeline_dropout(int kind, int io_dtype, const FwdParams& p, cudaStream_t st);
 // *reduced tells whether dgamma / dbeta / dgb_f32 were produced by the launch itself (fused
 // column reduce); otherwise the caller reduces p.partials.
 int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p, cudaStream_t st, bool* reduced);

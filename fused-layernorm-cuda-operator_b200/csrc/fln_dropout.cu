@@ -21,38 +21,9 @@
 //
 // Kernel: one CTA per row, the row in registers (K groups of 8 elements per thread), two-pass
 // statistics.  Non-persistent, so the hardware scheduler balances the rows.
-#include "fln_common.cuh"
+#include "fln_philox.cuh"
 
 namespace fln {
-
-__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const unsigned long long p0 = (unsigned long long)0xD2511F53u * c.x;
-    const unsigned long long p1 = (unsigned long long)0xCD9E8D57u * c.z;
-    c = make_uint4((unsigned int)(p1 >> 32) ^ c.y ^ k.x, (unsigned int)p1, (unsigned int)(p0 >> 32) ^ c.w ^ k.y,
-                   (unsigned int)p0);
-    k.x += 0x9E3779B9u;
-    k.y += 0xBB67AE85u;
-  }
-  return c;
-}
-
-// keep mask (8 bits) of group g
-__device__ __forceinline__ unsigned int keep_mask8(unsigned long long g, unsigned long long seed, unsigned long long offset,
-                                                   unsigned int threshold) {
-  const uint4 r = philox4x32_10(make_uint4((unsigned int)g, (unsigned int)(g >> 32), (unsigned int)offset,
-                                           (unsigned int)(offset >> 32)),
-                                make_uint2((unsigned int)seed, (unsigned int)(seed >> 32)));
-  const unsigned int w[4] = {r.x, r.y, r.z, r.w};
-  unsigned int m = 0;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const unsigned int v = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
-    m |= (v >= threshold ? 1u : 0u) << j;
-  }
-  return m;
-}
 
 struct DropParams {
   const void* x;
@@ -309,6 +280,40 @@ extern "C" int fln_dropout_add_norm_forward(int kind, const void* x, const void*
   q.seed = seed;
   q.offset = offset;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype != FLN_F32) {
+    // large 16-bit problems: the persistent pipelined forward with the dropout folded in
+    FwdParams f;
+    f.x = x;
+    f.res = residual;
+    f.gamma = gamma;
+    f.beta = beta;
+    f.y = y;
+    f.sum_out = sum_out;
+    f.mean = mean;
+    f.rstd = rstd;
+    f.rows = rows;
+    f.cols = (int)cols;
+    f.nv = 0;
+    f.tpr = 0;
+    f.log2_tpr = 0;
+    f.eps = eps;
+    f.sched = nullptr;
+    f.wait_ns = 0;
+    f.status = nullptr;
+    f.fault = nullptr;
+    f.q = nullptr;
+    f.scale_in = nullptr;
+    f.amax = nullptr;
+    f.block_scale = nullptr;
+    f.row_scale = nullptr;
+    f.keep_bits = keep_bits;
+    f.drop_seed = seed;
+    f.drop_offset = offset;
+    f.drop_threshold = q.threshold;
+    f.drop_scale = q.scale;
+    const int rc = launch_fwd_pipeline_dropout(kind, dtype, f, st);
+    if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+  }
 #define FLN_RUN(T) \
   (kind == FLN_LAYERNORM ? launch_drop_fwd<T, FLN_LAYERNORM>(q, st) : launch_drop_fwd<T, FLN_RMSNORM>(q, st))
   if (dtype == FLN_F32) return FLN_RUN(float);

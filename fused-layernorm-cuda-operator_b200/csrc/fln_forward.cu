@@ -391,6 +391,11 @@ extern "C" int fln_norm_forward(int kind, const void* x, const void* residual, c
   p.amax = nullptr;
   p.block_scale = nullptr;
   p.row_scale = nullptr;
+  p.keep_bits = nullptr;
+  p.drop_seed = 0;
+  p.drop_offset = 0;
+  p.drop_threshold = 0;
+  p.drop_scale = 1.f;
   const bool aligned = is_aligned16(x) && is_aligned16(y) && is_aligned16(residual) &&
                        is_aligned16(sum_out) && is_aligned16(gamma) && is_aligned16(beta);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

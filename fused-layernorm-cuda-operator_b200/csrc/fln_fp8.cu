@@ -555,6 +555,11 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
     f.amax = amax;
     f.block_scale = block_scale;
     f.row_scale = row_scale;
+    f.keep_bits = nullptr;
+    f.drop_seed = 0;
+    f.drop_offset = 0;
+    f.drop_threshold = 0;
+    f.drop_scale = 1.f;
     if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
     const int rc = launch_fwd_pipeline_fp8(kind, io_dtype, qmode == 0 ? 1 : qmode, f, st);
     if (rc == FLN_OK) {

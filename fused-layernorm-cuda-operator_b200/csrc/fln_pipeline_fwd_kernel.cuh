@@ -5,6 +5,7 @@
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
+#include "fln_philox.cuh"
 #include "fln_pipeline.cuh"
 
 namespace fln {
@@ -47,7 +48,12 @@ namespace fln {
 //   QM 4: NVFP4-style -- e2m1 codes, two per byte, one e4m3 scale per 16 elements (two
 //         neighbouring lanes), b = e4m3(block max * S / 6), q = e2m1(y * S / float(b)), S =
 //         *p.scale_in.
-template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1, int QM = 0>
+// DROP: dropout in front of the residual add -- x is replaced by round(x * scale) where the
+// Philox mask keeps it and by 0 elsewhere (one 128-bit Philox output per 16-byte vector; group,
+// counter and key as in fln_dropout.cu), the mask byte goes to p.keep_bits if that is set, and
+// the sum (or, without a residual, the dropped x) goes to p.sum_out if that is set.
+template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1, int QM = 0,
+          bool DROP = false>
 __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr int V2 = VEC / 2;
@@ -56,6 +62,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   constexpr bool TAIL = MODE == 5;
   constexpr bool Q8 = QM > 0;
   static_assert(QM == 0 || (VEC == 8 && MODE == 1), "quantized outputs: 16-bit input, 16-byte vectors, exact rows");
+  static_assert(!DROP || (VEC == 8 && MODE == 1), "dropout: 16-bit input, 16-byte vectors, exact rows");
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
@@ -187,6 +194,28 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
       } else {
 #pragma unroll
         for (int e = 0; e < V2; ++e) f[k][e] = f2(0.f);
+      }
+    }
+    if constexpr (DROP) {
+      const float2 sc2 = f2(p.drop_scale);
+      const unsigned long long g0 = (unsigned long long)row * (unsigned long long)(cols >> 3) + (unsigned int)lane_r;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const unsigned long long grp = g0 + (unsigned long long)(k * tpr);
+        unsigned int lanes[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        unsigned int m = 0xffu;
+        if (p.drop_threshold != 0) m = keep_lanes8(grp, p.drop_seed, p.drop_offset, p.drop_threshold, lanes);
+        if (p.keep_bits != nullptr) p.keep_bits[grp] = (unsigned char)m;
+#pragma unroll
+        for (int e = 0; e < V2; ++e) f[k][e] = f2mul(f[k][e], sc2);
+        Pack<TI, VEC> q;
+        pack2<TI, VEC>(f[k], q);  // rounds to the I/O type
+        unsigned int* w = reinterpret_cast<unsigned int*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[e] &= lanes[e];
+        if (!has_res && p.sum_out != nullptr)
+          st_stream<TI, VEC>(reinterpret_cast<TI*>(p.sum_out) + row * (int64_t)cols + (int64_t)(lane_r + k * tpr) * VEC, q);
+        unpack2<TI, VEC>(q, f[k]);
       }
     }
     if (has_res) {

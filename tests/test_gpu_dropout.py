@@ -57,6 +57,38 @@ def test_dropout_without_residual_and_without_stored_mask():
     U.assert_out_close(y.cpu(), w["y"], BF16)
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(1024, 8192, BF16), (2048, 1024, F16), (768, 3072, BF16), (512, 16384, BF16),
+                                             (1200, 768, F16)])
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("p", [0.1, 0.0])
+def test_dropout_through_the_pipelined_forward(rows, cols, dtype, kind, p):
+    """Large 16-bit problems run with the dropout folded into the persistent pipelined forward
+    (forced here for medium sizes): same mask bits, same residual stream, same checks; also
+    without a residual, with and without the dropped x written out."""
+    capi.lib().fln_set_path_override(2)
+    try:
+        test_dropout_add_norm_forward(rows, cols, dtype, kind, p)
+        x, gamma, beta, dy, _ = U.make_inputs(43, rows, cols, dtype)
+        if kind == "rmsnorm":
+            beta = None
+        d = lambda t: None if t is None else t.cuda()
+        bits = O.dropout_keep_bits(7, 11, p, rows * cols)
+        dropped = O.dropout_apply(x, bits, p)
+        w = O.norm_forward(dropped, gamma, beta, kind=kind)
+        for with_sum in (True, False):
+            y = U.Guarded((rows, cols), dtype)
+            s = U.Guarded((rows, cols), dtype) if with_sum else None
+            capi.dropout_add_norm_forward(U.KINDS[kind], d(x), None, d(gamma), d(beta), y.t, s.t if s else None, None,
+                                          None, None, 1e-5, p, 7, 11)
+            torch.cuda.synchronize()
+            U.assert_out_close(y.check().cpu(), w["y"], dtype)
+            if with_sum:
+                assert torch.equal(s.check().cpu(), dropped)
+        assert capi.lib().fln_device_status() == 0
+    finally:
+        capi.lib().fln_set_path_override(0)
+
+
 @pytest.mark.parametrize("dtype", [BF16, F32])
 @pytest.mark.parametrize("stored", [True, False])
 def test_dropout_backward_from_stored_or_regenerated_mask(dtype, stored):
