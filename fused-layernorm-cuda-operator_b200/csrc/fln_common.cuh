@@ -311,16 +311,70 @@ __device__ __forceinline__ void rowsum_cta(float (&v)[NV], int tpr, const float*
 // ------------------------------------------------------------------------------------
 // activations
 // ------------------------------------------------------------------------------------
+// GELU without tanhf / erff (25 - 30 instructions each, which made LayerNorm + GELU at 16384 x
+// 8192 bf16 twice as slow as LayerNorm alone: 173 / 191 against 87 us).
+//   tanh form: 0.5 v (1 + tanh(u)) = v / (1 + exp(-2u)), u = sqrt(2/pi) (v + 0.044715 v^3): one
+//   ex2.approx and one rcp.approx, relative error about 1e-6, and no cancellation for negative v
+//   (1 + tanh(u) loses every digit there).
+//   exact form: v Phi(v) with Phi from erfc(z) = (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z),
+//   z = |v| / sqrt(2) (Abramowitz & Stegun 7.1.26, absolute error 1.5e-7): Phi = erfc / 2 for
+//   negative v, 1 - erfc / 2 otherwise.
+// Both stay within the parity bounds (1e-5 absolute / relative in fp32, one unit in the last
+// place of a 16-bit output).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kGeluK = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2 sqrt(2/pi) log2(e)
+constexpr float kGeluKA = kGeluK * 0.044715f;
+constexpr float kErfP = 0.3275911f * 0.7071067811865476f;  // p / sqrt(2): t = 1 / (1 + kErfP |v|)
+constexpr float kErfE = -0.5f * 1.4426950408889634f;       // exp(-z^2) = 2^(kErfE v^2)
+// a1 .. a5 of 7.1.26, halved (Phi = erfc / 2)
+constexpr float kErfA1 = 0.5f * 0.254829592f, kErfA2 = 0.5f * -0.284496736f, kErfA3 = 0.5f * 1.421413741f,
+                kErfA4 = 0.5f * -1.453152027f, kErfA5 = 0.5f * 1.061405429f;
+
 template <int ACT>
 __device__ __forceinline__ float apply_act(float v) {
   if (ACT == FLN_ACT_GELU_TANH) {
-    // 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))
-    const float s = 0.7978845608028654f;
-    const float a = 0.044715f;
-    float v3 = v * v * v;
-    return 0.5f * v * (1.0f + tanhf(s * (v + a * v3)));
+    const float w = v * v;
+    const float e = ex2_approx(v * fmaf(w, kGeluKA, kGeluK));  // exp(-2u)
+    return v * rcp_approx(1.0f + e);
   } else if (ACT == FLN_ACT_GELU_ERF) {
-    return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+    const float t = rcp_approx(fmaf(fabsf(v), kErfP, 1.0f));
+    const float e = ex2_approx(v * v * kErfE);
+    const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, kErfA5, kErfA4), kErfA3), kErfA2), kErfA1);
+    const float h = poly * e;  // erfc(|v| / sqrt 2) / 2
+    return v * (v < 0.f ? h : 1.0f - h);
+  }
+  return v;
+}
+// the same on a register pair (packed fp32 arithmetic where the operation exists)
+template <int ACT>
+__device__ __forceinline__ float2 apply_act2(float2 v) {
+  if (ACT == FLN_ACT_GELU_TANH) {
+    const float2 w = f2mul(v, v);
+    const float2 a = f2mul(v, f2fma(w, f2(kGeluKA), f2(kGeluK)));
+    const float2 d = f2add(make_float2(ex2_approx(a.x), ex2_approx(a.y)), f2(1.0f));
+    return f2mul(v, make_float2(rcp_approx(d.x), rcp_approx(d.y)));
+  } else if (ACT == FLN_ACT_GELU_ERF) {
+    const float2 az = make_float2(fabsf(v.x), fabsf(v.y));
+    const float2 den = f2fma(az, f2(kErfP), f2(1.0f));
+    const float2 t = make_float2(rcp_approx(den.x), rcp_approx(den.y));
+    const float2 ea = f2mul(f2mul(v, v), f2(kErfE));
+    const float2 e = make_float2(ex2_approx(ea.x), ex2_approx(ea.y));
+    float2 poly = f2fma(t, f2(kErfA5), f2(kErfA4));
+    poly = f2fma(t, poly, f2(kErfA3));
+    poly = f2fma(t, poly, f2(kErfA2));
+    poly = f2fma(t, poly, f2(kErfA1));
+    const float2 h = f2mul(f2mul(poly, t), e);
+    const float2 up = f2add(f2(1.0f), make_float2(-h.x, -h.y));
+    return f2mul(v, make_float2(v.x < 0.f ? h.x : up.x, v.y < 0.f ? h.y : up.y));
   }
   return v;
 }

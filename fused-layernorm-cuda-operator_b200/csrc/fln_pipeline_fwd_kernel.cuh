@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
         }
         if (ACT != FLN_ACT_NONE) {
 #pragma unroll
-          for (int e = 0; e < V2; ++e) o[e] = make_float2(apply_act<ACT>(o[e].x), apply_act<ACT>(o[e].y));
+          for (int e = 0; e < V2; ++e) o[e] = apply_act2<ACT>(o[e]);
         }
         if constexpr (Q8) {
 #pragma unroll
