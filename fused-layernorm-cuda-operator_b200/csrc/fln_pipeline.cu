@@ -115,7 +115,9 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // Forward, 16-bit types: 40 or 48 elements per thread (K = 5 or 6 vectors of 8) with gamma /
   // beta parked in shared memory instead of registers.
   const bool wide_fwd = !backward && elem_bytes == 2 && allow_params_in_smem;
-  const int caps[2] = {backward ? (elem_bytes == 2 ? 20 : 16) : (wide_fwd ? 48 : 32),
+  // (24 columns at once for the plain 16-bit backward: its LayerNorm form parks the dbeta
+  // accumulators in shared memory, see `bsm` below, and then beats the 12-column plans)
+  const int caps[2] = {backward ? (elem_bytes == 2 ? (tensors == 2 ? 24 : 20) : 16) : (wide_fwd ? 48 : 32),
                        backward && elem_bytes == 2 ? 24 : 0};
   for (int pass = 0; pass < 2; ++pass) {
     const int cap_elems = caps[pass];
@@ -132,6 +134,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
         if (ck * cvec > cap_elems || cnv % ck != 0) continue;
         const int t = cnv / ck;
         if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
+        if (backward && ck * cvec == 24 && t < 64) continue;  // no 24-column instantiation for one-warp rows
         const int thr = t > cta_threads ? t : cta_threads;
         if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these
         if (ck * cvec > best_elems) {
@@ -210,7 +213,16 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
     // again with at most 32 elements per thread
     if (S < 2) return plan_pipeline(backward, rows, cols, elem_bytes, tensors, false, allow_tail);
   }
-  P.smem = kSmemHeader + (size_t)S * stage + (params_in_smem ? 2 * (size_t)row_bytes : 0);
+  // 16-bit backward with 24 columns per thread: the dbeta accumulators (12 float2 per thread)
+  // go behind the stages; the LayerNorm instantiation uses them, RMSNorm has none
+  bool bsm = backward && elem_bytes == 2 && vb == 16 && K == 3 && threads == 512 && tensors == 2 && P.full;
+  size_t bsm_bytes = bsm ? (size_t)12 * 512 * sizeof(float2) : 0;
+  if ((size_t)kSmemHeader + (size_t)S * stage + bsm_bytes > 220 * 1024) {
+    bsm = false;
+    bsm_bytes = 0;
+  }
+  P.bsm = bsm;
+  P.smem = kSmemHeader + (size_t)S * stage + (params_in_smem ? 2 * (size_t)row_bytes : 0) + bsm_bytes;
   P.g.R = R;
   P.g.tpr = tpr;
   P.g.log2_tpr = ilog2i(tpr);

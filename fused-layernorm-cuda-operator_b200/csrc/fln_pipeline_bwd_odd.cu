@@ -10,6 +10,19 @@ static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) 
   constexpr int VEC = VB / (int)sizeof(T);
   if constexpr (VEC >= 2 && KK * VEC <= (sizeof(T) == 2 ? 24 : 16)) {
     const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
+    // 24 columns per thread, LayerNorm: the dbeta accumulators in shared memory
+    if constexpr (KIND == FLN_LAYERNORM && sizeof(T) == 2 && KK == 3 && VB == 16) {
+      if (!dr && P.bsm && P.threads == 512) {
+#define FLN_BSM_LT(L)                                                                                                       \
+  if (P.g.tpr == (1 << L)) {                                                                                                \
+    if (fuse)                                                                                                               \
+      return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, L, false, false, true>, p, P, st); \
+    return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, L, false, false, true>, p, P, st);  \
+  }
+        FLN_BSM_LT(9) FLN_BSM_LT(8) FLN_BSM_LT(7) FLN_BSM_LT(6)
+#undef FLN_BSM_LT
+      }
+    }
     // geometry as template arguments for rows of 64 to 512 threads (no residual-stream gradient)
     if (!dr && P.threads == 512) {
 #define FLN_ODD_LT(L)                                                                                              \
