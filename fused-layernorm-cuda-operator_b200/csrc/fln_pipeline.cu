@@ -117,7 +117,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   const bool wide_fwd = !backward && elem_bytes == 2 && allow_params_in_smem;
   // (24 columns at once for the plain 16-bit backward: its LayerNorm form parks the dbeta
   // accumulators in shared memory, see `bsm` below, and then beats the 12-column plans)
-  const int caps[2] = {backward ? (elem_bytes == 2 ? (tensors == 2 ? 24 : 20) : 16) : (wide_fwd ? 48 : 32),
+  const int caps[2] = {backward ? (elem_bytes == 2 ? (tensors == 2 ? 24 : 20) : (tensors == 2 ? 20 : 16))
+                                : (wide_fwd ? 48 : 32),
                        backward && elem_bytes == 2 ? 24 : 0};
   for (int pass = 0; pass < 2; ++pass) {
     const int cap_elems = caps[pass];
@@ -135,6 +136,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
         const int t = cnv / ck;
         if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
         if (backward && ck * cvec == 24 && t < 64) continue;  // no 24-column instantiation for one-warp rows
+        if (backward && elem_bytes == 4 && ck * cvec == 20 && t != 512) continue;  // fp32, 20 columns: 10240 only
         const int thr = t > cta_threads ? t : cta_threads;
         if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these
         if (ck * cvec > best_elems) {
@@ -215,8 +217,10 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   }
   // 16-bit backward with 24 columns per thread: the dbeta accumulators (12 float2 per thread)
   // go behind the stages; the LayerNorm instantiation uses them, RMSNorm has none
-  bool bsm = backward && elem_bytes == 2 && vb == 16 && K == 3 && threads == 512 && tensors == 2 && P.full;
-  size_t bsm_bytes = bsm ? (size_t)12 * 512 * sizeof(float2) : 0;
+  // (and the fp32 backward with 20 columns per thread, 10240 columns)
+  bool bsm = backward && vb == 16 && threads == 512 && tensors == 2 && P.full &&
+             ((elem_bytes == 2 && K == 3) || (elem_bytes == 4 && K == 5));
+  size_t bsm_bytes = bsm ? (size_t)(K * (16 / elem_bytes) / 2) * 512 * sizeof(float2) : 0;
   if ((size_t)kSmemHeader + (size_t)S * stage + bsm_bytes > 220 * 1024) {
     bsm = false;
     bsm_bytes = 0;
@@ -283,7 +287,7 @@ PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
   PipePlan P = plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
   if (!P.ok && !with_dres && cols % 2 == 0 && g_path_override.load(std::memory_order_relaxed) != 3) {
     PipePlan H = plan_pipeline(true, rows, cols / 2, es, 2);
-    if (H.ok && H.full && H.threads == 512 && H.g.tpr == 512 && H.g.R == 1 && H.K * (H.vb / es) <= 20) {
+    if (H.ok && H.full && !H.bsm && H.threads == 512 && H.g.tpr == 512 && H.g.R == 1 && H.K * (H.vb / es) <= 20) {
       H.pair = true;
       const int64_t slots = pair_slots();
       H.grid = (int)(2 * (rows < slots ? rows : slots));

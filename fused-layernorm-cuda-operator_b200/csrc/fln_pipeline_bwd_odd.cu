@@ -8,10 +8,13 @@ namespace fln {
 template <typename T, int KIND, int KK, int VB>
 static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   constexpr int VEC = VB / (int)sizeof(T);
-  if constexpr (VEC >= 2 && KK * VEC <= (sizeof(T) == 2 ? 24 : 16)) {
+  // fp32 with 20 columns per thread: LayerNorm only with its dbeta accumulators in shared memory
+  // (below), RMSNorm has none
+  constexpr int kMaxCols = sizeof(T) == 2 ? 24 : ((KK == 5 && VB == 16) ? 20 : 16);
+  if constexpr (VEC >= 2 && KK * VEC <= kMaxCols) {
     const bool fuse = p.sync != nullptr, dr = p.dres_in != nullptr;
     // 24 columns per thread, LayerNorm: the dbeta accumulators in shared memory
-    if constexpr (KIND == FLN_LAYERNORM && sizeof(T) == 2 && KK == 3 && VB == 16) {
+    if constexpr (KIND == FLN_LAYERNORM && VB == 16 && ((sizeof(T) == 2 && KK == 3) || (sizeof(T) == 4 && KK == 5))) {
       if (!dr && P.bsm && P.threads == 512) {
 #define FLN_BSM_LT(L)                                                                                                       \
   if (P.g.tpr == (1 << L)) {                                                                                                \
@@ -23,6 +26,7 @@ static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) 
 #undef FLN_BSM_LT
       }
     }
+    if constexpr (KIND == FLN_LAYERNORM && sizeof(T) == 4 && KK * VEC > 16) return FLN_PIPE_NOT_APPLICABLE;
     // geometry as template arguments for rows of 64 to 512 threads (no residual-stream gradient)
     if (!dr && P.threads == 512) {
 #define FLN_ODD_LT(L)                                                                                              \
@@ -47,7 +51,7 @@ static int bwd_pipe_odd_k(const BwdParams& p, const PipePlan& P, cudaStream_t st
   if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_ODD(KK, VBB) \
   if (P.K == KK && P.vb == VBB) return bwd_pipe_odd<T, KIND, KK, VBB>(p, P, st);
-  FLN_ODD(3, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8) FLN_ODD(3, 4) FLN_ODD(5, 4) FLN_ODD(7, 4)
+  FLN_ODD(3, 16) FLN_ODD(5, 16) FLN_ODD(3, 8) FLN_ODD(5, 8) FLN_ODD(7, 8) FLN_ODD(3, 4) FLN_ODD(5, 4) FLN_ODD(7, 4)
 #undef FLN_ODD
   return FLN_PIPE_NOT_APPLICABLE;
 }

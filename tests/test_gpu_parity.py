@@ -647,7 +647,7 @@ def test_long_rows_backward(shape, dtype, kind):
 
 
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
-@pytest.mark.parametrize("dtype,shape", [(BF16, (1200, 16384)), (BF16, (700, 14336)), (F32, (900, 10240)),
+@pytest.mark.parametrize("dtype,shape", [(BF16, (1200, 16384)), (BF16, (700, 14336)),
                                          (F32, (640, 16384)), (F16, (800, 20480)), (F32, (600, 12288)),
                                          (F32, (500, 14336))])
 def test_rows_shared_by_the_two_ctas_of_a_cluster(path_override, shape, dtype, kind):
@@ -701,11 +701,13 @@ def test_pipelined_backward_adds_residual_gradient_in_place():
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype", [BF16, F32, F16])
 @pytest.mark.parametrize("shape", [(2048, 768), (1536, 1280), (1024, 2560), (640, 3072), (600, 5120), (304, 6144),
-                                   (300, 7168), (296, 12288), (2049, 768)])
+                                   (300, 7168), (296, 12288), (2049, 768), (1024, 1536), (450, 10240)])
 def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape, dtype, kind):
     """Hidden sizes such as 768, 1280, 5120, 12288 divide evenly over the threads only with an
     odd number of vectors per thread and, for some, shorter vectors; those plans exist in the
-    pipelined kernels.  (2049 rows: not a whole number of row groups, so the padded plan runs.)"""
+    pipelined kernels.  (2049 rows: not a whole number of row groups, so the padded plan runs;
+    1536 ... 12288 columns in 16-bit types and 10240 in fp32: the LayerNorm backward keeps its
+    dbeta accumulators in shared memory.)"""
     path_override(2)
     rows, cols = shape
     x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 5, rows, cols, dtype, residual=True)
