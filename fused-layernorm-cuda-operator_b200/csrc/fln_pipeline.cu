@@ -285,6 +285,29 @@ void set_pair_slots(int n) {
 // half row, one row per tile) with `pair` set and the grid counted in CTAs (two per row slot).
 PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
   PipePlan P = plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
+  // 16-bit rows of 16384 columns: one CTA per row, two passes over the staged row
+  // (fln_pipeline_bwd_wide.cu); two stages of dy + x and the dbeta accumulators behind them
+  if (!P.ok && !with_dres && es == 2 && (cols == 16384 || cols == 14336) && rows > 0 &&
+      g_path_override.load(std::memory_order_relaxed) != 3) {
+    PipePlan W;
+    memset(&W, 0, sizeof(W));
+    W.ok = true;
+    W.wide = true;
+    W.vb = cols == 16384 ? 16 : 8;
+    W.K = cols == 16384 ? 4 : 7;
+    W.threads = 512;
+    W.g.R = 1;
+    W.g.tpr = 512;
+    W.g.log2_tpr = 9;
+    W.g.S = 2;
+    W.g.row_bytes = (uint32_t)cols * 2;
+    W.g.second_off = W.g.row_bytes;
+    W.g.stage_stride = 2 * W.g.row_bytes;
+    W.smem = (size_t)kSmemHeader + 2 * (size_t)W.g.stage_stride + (size_t)(cols / 1024) * 512 * sizeof(float2);
+    const int64_t cap = usable_sms();
+    W.grid = (int)(rows < cap ? rows : cap);
+    return W;
+  }
   if (!P.ok && !with_dres && cols % 2 == 0 && g_path_override.load(std::memory_order_relaxed) != 3) {
     PipePlan H = plan_pipeline(true, rows, cols / 2, es, 2);
     if (H.ok && H.full && !H.bsm && H.threads == 512 && H.g.tpr == 512 && H.g.R == 1 && H.K * (H.vb / es) <= 20) {
@@ -306,7 +329,7 @@ bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, Pi
     if (!rp.generic && rp.vec == 4 && (int64_t)rp.K * rp.tpr * rp.vec == cols) return false;
   }
   // the odd plans exist only as branch-free instantiations; K = 8 only for fp32 forward
-  if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) && !P.full && !P.tail) return false;
+  if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) && !P.full && !P.tail && !P.wide) return false;
   out->vector_bytes = P.vb;
   out->K = P.K;
   out->tpr = P.g.tpr;

@@ -78,7 +78,7 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
   p.fault = w.fault;
   // Fused column reduce: one CTA per SM (so the whole grid is resident at once), the
   // one-row kernel, stage memory large enough for the 16 x 128 floats of the combine step.
-  const bool fuse = !P.pair && p.sync != nullptr && p.partials != nullptr && P.grid <= usable_sms() &&
+  const bool fuse = !P.pair && !P.wide && p.sync != nullptr && p.partials != nullptr && P.grid <= usable_sms() &&
                     P.grid < 4096 && P.smem >= (size_t)kSmemHeader + 16 * 128 * sizeof(float) &&
                     path_override() != 3 && cooperative_launch_supported();
   if (fuse) {
@@ -91,7 +91,8 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
   const bool shared_row = P.pair || P.tail;
   const bool odd = P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7;
 #define FLN_RUN(T)                                                                          \
-  (shared_row ? bwd_pipe_pair_any(kind, dtype, p, P, st)                                    \
+  (P.wide ? bwd_pipe_wide_any(kind, dtype, p, P, st) :                                      \
+   shared_row ? bwd_pipe_pair_any(kind, dtype, p, P, st)                                    \
               : (odd ? bwd_pipe_odd_any(kind, dtype, p, P, st)                              \
                      : (kind == FLN_LAYERNORM ? bwd_pipe_k<T, FLN_LAYERNORM>(p, P, st)      \
                                               : bwd_pipe_k<T, FLN_RMSNORM>(p, P, st))))

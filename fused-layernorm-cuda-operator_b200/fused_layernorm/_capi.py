@@ -33,7 +33,7 @@ SYMBOLS = [
     "fln_planner_selftest", "fln_sum_rows_f32", "fln_set_stage_override", "fln_set_wait_limit_ns",
     "fln_set_test_fault", "fln_set_static_scratch_limit", "fln_norm_backward_partial", "fln_dropout_add_norm_forward", "fln_dropout_backward", "fln_norm_forward_nvfp4",
 ]
-STATIC_SCRATCH_BYTES = 16 << 20  # FLN_STATIC_SCRATCH_BYTES
+STATIC_SCRATCH_BYTES = 24 << 20  # FLN_STATIC_SCRATCH_BYTES
 
 
 class LaunchInfo(C.Structure):

@@ -77,7 +77,7 @@ def test_static_scratch_after_a_larger_plan_left_data_under_the_barrier_word():
 
 
 def test_static_scratch_refuses_problems_beyond_its_capacity():
-    """No plan of the launcher needs more than 14.5 MB on a B200 (checked over a grid of shapes),
+    """No plan of the launcher needs more than 19.4 MB on a B200 (checked over a grid of shapes),
     so the refusal is exercised by lowering the accepted size with the library's own hook: the
     call must return the static-scratch error and launch nothing."""
     L = capi.lib()
