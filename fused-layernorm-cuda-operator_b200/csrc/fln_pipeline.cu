@@ -188,7 +188,14 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // CTAs per SM by design: the 512-thread kernels are capped at 128 registers per thread by
   // their launch bounds and use most of them, so one such CTA fills an SM's register file and
   // two 256-thread CTAs do
-  const int ctas_per_sm = threads >= 512 ? 1 : 2;
+  // 16-bit forward rows of 16384 columns (512 threads, 4 vectors each): two CTAs per SM (64
+  // registers each) with gamma / beta fetched per row (plain forward only): 5420 -> 5884 GB/s.
+  // With 5 or 6 vectors per thread the same form was slower than one CTA per SM (bf16 20480:
+  // 5072 against 5831 GB/s, fp32 12288: 5108 against 5727; fp32 10240 unchanged).
+  const bool pgl = !backward && allow_tail && !tail && threads == 512 && tpr == 512 && tensors == 1 && vb == 16 &&
+                   elem_bytes == 2 && K == 4 && (int64_t)K * tpr == cols / (vb / elem_bytes) &&
+                   (size_t)kSmemHeader + 2 * (size_t)stage <= 100 * 1024;
+  const int ctas_per_sm = (threads >= 512 && !pgl) ? 1 : 2;
   const size_t budget = (size_t)(200 * 1024) / ctas_per_sm;
   const size_t in_flight = (size_t)(96 * 1024) / ctas_per_sm;
   int S_fit = (int)((budget - kSmemHeader) / stage);
@@ -203,11 +210,12 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   P.ok = true;
   P.full = tpr >= 32 && (int64_t)K * tpr == cols / (vb / elem_bytes) && rows % R == 0;
   P.tail = tail;
+  P.pgl = pgl;
   P.vb = vb;
   P.K = K;
   P.threads = threads;
   // forward plans beyond 32 elements per thread keep gamma and beta behind the stages
-  const bool params_in_smem = !backward && K * (vb / elem_bytes) > 32;
+  const bool params_in_smem = !backward && !pgl && K * (vb / elem_bytes) > 32;
   if (params_in_smem) {
     const int room = (int)((budget - kSmemHeader - 2 * (size_t)row_bytes) / stage);
     if (S > room) S = room;

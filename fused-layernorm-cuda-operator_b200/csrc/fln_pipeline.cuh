@@ -251,6 +251,7 @@ struct PipePlan {
   bool tail;  // rows are whole but the last of a thread's K vectors is ragged (lanes beyond the row idle)
   bool bsm;   // backward only: the dbeta accumulators live in shared memory behind the stages (24-column plans)
   bool wide;  // backward only: 16-bit rows of 16384 columns, one CTA per row in two passes over the stage
+  bool pgl;   // forward only: 512 threads per row, gamma / beta fetched per row, two CTAs per SM
   int vb;     // bytes per vector: 16, or 8 / 4 where that makes the row divide evenly
   int K;
   int threads;

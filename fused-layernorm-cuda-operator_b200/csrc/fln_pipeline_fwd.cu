@@ -60,9 +60,32 @@ static int fwd_pipe_tail(const FwdParams& p, const PipePlan& P, cudaStream_t st)
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
+// rows of 512 threads with two CTAs per SM (plan_pipeline's `pgl` plans): 4 vectors of 16 bytes
+// per thread in 16-bit types, gamma / beta fetched per row; plain forward only
+template <typename TI, typename TO, int KIND, int ACT>
+static int fwd_pipe_pgl(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
+    if (P.vb != 16 || P.threads != 512 || P.g.tpr != 512) return FLN_PIPE_NOT_APPLICABLE;
+#define FLN_GO(KK)                                                                                  \
+  if (P.K == KK) {                                                                                  \
+    if constexpr (sizeof(TI) == 2) {                                                                \
+      auto kern = norm_fwd_pipe_kernel<TI, TO, KK, KIND, ACT, 6, 16, 9>;                            \
+      if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;                                  \
+      kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                                              \
+      FLN_CHECK_LAUNCH();                                                                           \
+      return FLN_OK;                                                                                \
+    }                                                                                               \
+  }
+    FLN_GO(4)
+#undef FLN_GO
+  }
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
 template <typename TI, typename TO, int KIND, int ACT>
 static int fwd_pipe_k(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   if (P.tail) return fwd_pipe_tail<TI, TO, KIND, ACT>(p, P, st);
+  if (P.pgl) return fwd_pipe_pgl<TI, TO, KIND, ACT>(p, P, st);
   if (P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) {
     if (!P.full) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_ODD(KK, VBB) \

@@ -54,11 +54,16 @@ namespace fln {
 // the sum (or, without a residual, the dropped x) goes to p.sum_out if that is set.
 template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB = 16, int LT = -1, int QM = 0,
           bool DROP = false>
-__global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
+// MODE 6: FULL with gamma / beta fetched from global memory (L1 / L2) for every row instead of
+// living in registers, and the kernel held to 64 registers: two 512-thread CTAs per SM for rows
+// that need 512 threads (one CTA of 512 threads per SM walks its rows in lockstep at a quarter
+// of the warp slots).
+__global__ void __launch_bounds__(512, MODE == 6 ? 2 : 1) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr int V2 = VEC / 2;
   constexpr bool FULL = MODE >= 1;
   constexpr bool PSM = MODE == 4;
+  constexpr bool PGL = MODE == 6;
   constexpr bool TAIL = MODE == 5;
   constexpr bool Q8 = QM > 0;
   static_assert(QM == 0 || (VEC == 8 && MODE == 1), "quantized outputs: 16-bit input, 16-byte vectors, exact rows");
@@ -66,7 +71,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
-  static_assert(!CT || MODE == 1 || MODE == 4 || MODE == 5, "compile-time geometry is for the FULL kernels");
+  static_assert(!CT || MODE == 1 || MODE == 4 || MODE == 5 || MODE == 6, "compile-time geometry is for the FULL kernels");
   static_assert(!TAIL || CT, "the ragged-last-vector kernel has its split at compile time");
 // vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
 #define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
@@ -126,7 +131,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
     next_t = dyn_base + atomicAdd(sched, 1u);
   }
 
-  float2 gam[PSM ? 1 : K][V2], bet[PSM ? 1 : K][V2];
+  float2 gam[(PSM || PGL) ? 1 : K][V2], bet[(PSM || PGL) ? 1 : K][V2];
   bool vok[K];  // does vector k of this thread exist in the row
   unsigned char* s_gamma = stages + (size_t)S * g.stage_stride;  // PSM: [cols] gamma, then [cols] beta
   unsigned char* s_beta = s_gamma + row_bytes;
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
         *reinterpret_cast<Pack<TI, VEC>*>(s_beta + (size_t)iv * VB) =
             p.beta != nullptr ? ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + (int64_t)iv * VEC) : zero;
       }
-    } else {
+    } else if constexpr (!PGL) {
 #pragma unroll
       for (int e = 0; e < V2; ++e) {
         gam[k][e] = f2(1.f);
@@ -350,6 +355,18 @@ __global__ void __launch_bounds__(512) norm_fwd_pipe_kernel(const FwdParams p, c
           const size_t po = (size_t)(lane_r + k * tpr) * VB;
           unpack2<TI, VEC>(stage_vec<TI, VEC>(s_gamma + po), gw);
           unpack2<TI, VEC>(stage_vec<TI, VEC>(s_beta + po), bw);
+#pragma unroll
+          for (int e = 0; e < V2; ++e) o[e] = f2fma(f2mul(f[k][e], r2), gw[e], bw[e]);
+        } else if constexpr (PGL) {
+          float2 gw[V2], bw[V2];
+#pragma unroll
+          for (int e = 0; e < V2; ++e) {
+            gw[e] = f2(1.f);
+            bw[e] = f2(0.f);
+          }
+          const int64_t po = (int64_t)(lane_r + k * tpr) * VEC;
+          if (p.gamma != nullptr) unpack2<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.gamma) + po), gw);
+          if (p.beta != nullptr) unpack2<TI, VEC>(ld_param<TI, VEC>(reinterpret_cast<const TI*>(p.beta) + po), bw);
 #pragma unroll
           for (int e = 0; e < V2; ++e) o[e] = f2fma(f2mul(f[k][e], r2), gw[e], bw[e]);
         } else {
