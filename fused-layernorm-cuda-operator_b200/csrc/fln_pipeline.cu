@@ -135,7 +135,6 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
         if (ck * cvec > cap_elems || cnv % ck != 0) continue;
         const int t = cnv / ck;
         if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
-        if (backward && ck * cvec == 24 && t < 64) continue;  // no 24-column instantiation for one-warp rows
         if (backward && elem_bytes == 4 && ck * cvec == 20 && t != 512) continue;  // fp32, 20 columns: 10240 only
         const int thr = t > cta_threads ? t : cta_threads;
         if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these

@@ -22,19 +22,19 @@ static int bwd_pipe_odd(const BwdParams& p, const PipePlan& P, cudaStream_t st) 
       return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, L, false, false, true>, p, P, st); \
     return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, L, false, false, true>, p, P, st);  \
   }
-        FLN_BSM_LT(9) FLN_BSM_LT(8) FLN_BSM_LT(7) FLN_BSM_LT(6)
+        FLN_BSM_LT(9) FLN_BSM_LT(8) FLN_BSM_LT(7) FLN_BSM_LT(6) FLN_BSM_LT(5)
 #undef FLN_BSM_LT
       }
     }
     if constexpr (KIND == FLN_LAYERNORM && sizeof(T) == 4 && KK * VEC > 16) return FLN_PIPE_NOT_APPLICABLE;
-    // geometry as template arguments for rows of 64 to 512 threads (no residual-stream gradient)
+    // geometry as template arguments for rows of 32 to 512 threads (no residual-stream gradient)
     if (!dr && P.threads == 512) {
 #define FLN_ODD_LT(L)                                                                                              \
   if (P.g.tpr == (1 << L)) {                                                                                       \
     if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, L>, p, P, st);     \
     return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, L>, p, P, st);              \
   }
-      FLN_ODD_LT(9) FLN_ODD_LT(8) FLN_ODD_LT(7) FLN_ODD_LT(6)
+      FLN_ODD_LT(9) FLN_ODD_LT(8) FLN_ODD_LT(7) FLN_ODD_LT(6) FLN_ODD_LT(5)
 #undef FLN_ODD_LT
     }
     if (fuse && dr) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB>, p, P, st);
