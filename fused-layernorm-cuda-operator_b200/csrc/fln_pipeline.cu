@@ -134,7 +134,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
         if (ck == 4 || (ck == 6 && (backward || cvb != 16))) continue;
         if (ck * cvec > cap_elems || cnv % ck != 0) continue;
         const int t = cnv / ck;
-        if (t < 32 || t > 512 || (t & (t - 1)) != 0) continue;
+        // (half-warp rows only for the 48-element forward plan: 768 columns in 16-bit types)
+        if (t < ((wide_fwd && ck == 6) ? 16 : 32) || t > 512 || (t & (t - 1)) != 0) continue;
         if (backward && elem_bytes == 4 && ck * cvec == 20 && t != 512) continue;  // fp32, 20 columns: 10240 only
         const int thr = t > cta_threads ? t : cta_threads;
         if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these
@@ -207,7 +208,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   if (fS >= 2) S = fS;
   if (S > S_fit) S = S_fit;
   P.ok = true;
-  P.full = tpr >= 32 && (int64_t)K * tpr == cols / (vb / elem_bytes) && rows % R == 0;
+  P.full = (tpr >= 32 || (!backward && K == 6 && tpr == 16)) && (int64_t)K * tpr == cols / (vb / elem_bytes) &&
+           rows % R == 0;
   P.tail = tail;
   P.pgl = pgl;
   P.vb = vb;

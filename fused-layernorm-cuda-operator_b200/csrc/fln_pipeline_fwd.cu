@@ -24,6 +24,7 @@ static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) 
     if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
       const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
       if (P.threads == nt) {
+        if (P.g.tpr == 16) FLN_GO(4)
         if (P.g.tpr == 32) FLN_GO(5)
         if (P.g.tpr == 64) FLN_GO(6)
         if (P.g.tpr == 128) FLN_GO(7)
