@@ -139,6 +139,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
         if (backward && elem_bytes == 4 && ck * cvec == 20 && t != 512) continue;  // fp32, 20 columns: 10240 only
         const int thr = t > cta_threads ? t : cta_threads;
         if (rows % (thr / t) != 0) continue;  // only the branch-free kernel exists for these
+        // half-warp rows make tiles of 16 rows: only where every CTA still streams four of them
+        if (t == 16 && rows / (thr / t) < 8LL * usable_sms()) continue;
         if (ck * cvec > best_elems) {
           best_elems = ck * cvec;
           K = ck;
