@@ -157,7 +157,9 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // vectors 0 .. 5 are whole (the `tail` instantiations); rows must fill the CTA's row slots.
   bool tail = false;
   if (allow_tail && fK == 0 && tensors <= 2 && (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes))) {
-    const int cap_elems = backward ? (elem_bytes == 2 ? 20 : 16) : 32;
+    // (forward, 16-bit types: 56 elements per thread in 16-byte vectors with gamma / beta in
+    // shared memory, where that is allowed)
+    const int cap_elems = backward ? (elem_bytes == 2 ? 20 : 16) : (wide_fwd ? 56 : 32);
     const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
     for (int cvb = 16; cvb >= min_vb && !tail; cvb >>= 1) {
       const int cvec = cvb / elem_bytes;

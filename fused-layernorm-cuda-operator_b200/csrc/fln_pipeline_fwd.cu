@@ -46,7 +46,24 @@ static int fwd_pipe_tail(const FwdParams& p, const PipePlan& P, cudaStream_t st)
   if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
     constexpr int VB = sizeof(TI) == 2 ? 8 : 16;
     const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
-    if (P.K != 7 || P.vb != VB || P.threads != nt) return FLN_PIPE_NOT_APPLICABLE;
+    if (P.K != 7 || P.threads != nt) return FLN_PIPE_NOT_APPLICABLE;
+    // 16-bit types, 16-byte vectors: 56 elements per thread, gamma / beta in shared memory
+    if constexpr (sizeof(TI) == 2) {
+      if (P.vb == 16) {
+#define FLN_GO7(LTT)                                                         \
+  if (P.g.tpr == (1 << LTT)) {                                               \
+    auto kern = norm_fwd_pipe_kernel<TI, TO, 7, KIND, ACT, 7, 16, LTT>;      \
+    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;             \
+    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                         \
+    FLN_CHECK_LAUNCH();                                                      \
+    return FLN_OK;                                                           \
+  }
+        FLN_GO7(5) FLN_GO7(6) FLN_GO7(7) FLN_GO7(8) FLN_GO7(9)
+#undef FLN_GO7
+        return FLN_PIPE_NOT_APPLICABLE;
+      }
+    }
+    if (P.vb != VB) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_GO(LTT)                                                          \
   if (P.g.tpr == (1 << LTT)) {                                               \
     auto kern = norm_fwd_pipe_kernel<TI, TO, 7, KIND, ACT, 5, VB, LTT>;      \
