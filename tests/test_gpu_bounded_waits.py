@@ -177,3 +177,36 @@ def test_cluster_pair_gives_up_together_and_the_next_call_is_correct(hooks):
         U.assert_param_grads_close(dgb.cpu(), torch.cat([want["dgamma64"], want["dbeta64"]]), want["abs64"].reshape(-1), rows)
     finally:
         hooks.fln_set_path_override(0)
+
+
+def test_two_pass_backward_gives_up_and_the_next_call_is_correct(hooks):
+    """16-bit rows of 16384 columns (one CTA per row, two passes over the staged row): CTA 0 never
+    gets its first copy, its wait runs out, the launch returns with status 1, and the next call
+    is correct."""
+    rows, cols = 600, 16384
+    hooks.fln_set_path_override(2)
+    try:
+        d = capi.describe_launch(True, rows, cols, BF16)
+        assert d["pipelined"] == 1 and d["vecs_per_thread"] == 4 and d["threads_per_row"] == 512 and d["stages"] == 2
+        x, gamma, beta, dy, _ = U.make_inputs(12, rows, cols, BF16)
+        f = O.norm_forward(x, gamma, beta)
+        dev = [t.cuda() for t in (dy, x, f["mean"], f["rstd"], gamma)]
+        dx = torch.zeros(rows, cols, dtype=BF16, device="cuda")
+        dgb = torch.empty(2 * cols, device="cuda")
+        ws = torch.empty(capi.backward_workspace_bytes(rows, cols, BF16) // 4, device="cuda")
+        run = lambda: capi.norm_backward(capi.LAYERNORM, dev[0], dev[1], dev[2], dev[3], dev[4], None, dx, None, None,
+                                         dgb, ws)
+        hooks.fln_set_test_fault(1)
+        run()
+        torch.cuda.synchronize()
+        assert hooks.fln_device_status() == 1
+        hooks.fln_set_test_fault(0)
+        dx.zero_()
+        run()
+        torch.cuda.synchronize()
+        assert hooks.fln_device_status() == 0
+        want = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma)
+        U.assert_out_close(dx.cpu(), want["dx"], BF16)
+        U.assert_param_grads_close(dgb.cpu(), torch.cat([want["dgamma64"], want["dbeta64"]]), want["abs64"].reshape(-1), rows)
+    finally:
+        hooks.fln_set_path_override(0)
