@@ -24,7 +24,7 @@ INCLUDE = ROOT / "include"
 OBJ = HERE / "build"
 LIB = HERE / "libfln_b200.so"
 
-CU_SOURCES = ["fln_pipeline_bwd_odd.cu", "fln_pipeline_bwd.cu", "fln_pipeline_bwd_pair.cu", "fln_pipeline_bwd_wide.cu", "fln_pipeline_fwd.cu", "fln_pipeline_fwd_fp8.cu", "fln_pipeline_fwd_drop.cu", "fln_forward.cu", "fln_backward.cu", "fln_fp8.cu", "fln_host.cu",
+CU_SOURCES = ["fln_pipeline_bwd_tail_bf16.cu", "fln_pipeline_bwd_tail_f16.cu", "fln_pipeline_bwd_tail_f32.cu", "fln_pipeline_bwd_odd.cu", "fln_pipeline_bwd.cu", "fln_pipeline_bwd_pair.cu", "fln_pipeline_bwd_wide.cu", "fln_pipeline_fwd.cu", "fln_pipeline_fwd_tail_bf16.cu", "fln_pipeline_fwd_tail_f16.cu", "fln_pipeline_fwd_tail_f32.cu", "fln_pipeline_fwd_fp8.cu", "fln_pipeline_fwd_drop.cu", "fln_forward.cu", "fln_backward.cu", "fln_fp8.cu", "fln_host.cu",
               "fln_pipeline.cu", "fln_static.cu", "fln_dropout.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -150,26 +150,42 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
       }
     }
   }
-  // Rows that fit none of the exact plans (1600 = 25 * 64 columns): K = 7 vectors on the
-  // power-of-two number of threads that leaves only the last vector ragged -- at most a seventh
-  // of the lanes idle in it, against up to half the lanes of the padded power-of-two plan -- in
-  // the widest vectors the register budget allows.  The kernels know at compile time that
-  // vectors 0 .. 5 are whole (the `tail` instantiations); rows must fill the CTA's row slots.
+  // Rows that fit none of the exact plans (1600 = 25 * 64, 4608 = 9 * 512, 5376 = 21 * 256
+  // columns ...): K vectors on the power-of-two number of threads for which only the last
+  // vector is ragged, (K - 1) t < vectors per row <= K t -- at most 1 / K of the lanes idle in
+  // that one vector, against up to half of all lanes in the padded power-of-two plan.  The
+  // first candidate that fits is taken: most elements per thread first, except that the
+  // backward prefers seven short vectors to four of twice the length where both fit (fewer idle
+  // lanes in the last vector; bf16 1600 / 3200 / 6400 / 3456 columns: 5701 / 5684 / 5450 / 5952
+  // against 5505 / 5550 / 5373 / 5822 GB/s; fp32 within 3 % either way except 3200 columns,
+  // 6385 against 5903).  The kernels know at compile time that vectors 0 .. K - 2 are whole
+  // (the `tail` instantiations); rows must fill the CTA's row slots.  The (K, bytes per vector)
+  // pairs are the ones instantiated:
+  //   forward   fp32    16 B x 8 .. 3                          (32 .. 12 elements)
+  //             16-bit  16 B x 7 .. 5, gamma / beta in shared memory (56 .. 40), 16 B x 4, 8 B x 7, 16 B x 3
+  //   backward  fp32    8 B x 7, 16 B x 4, 3, 8 B x 5          (10 .. 16 columns)
+  //             16-bit  4 B x 7, 8 B x 5, 4, 3                 (12 .. 20 columns)
   bool tail = false;
   if (allow_tail && fK == 0 && tensors <= 2 && (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes))) {
-    // (forward, 16-bit types: 56 elements per thread in 16-byte vectors with gamma / beta in
-    // shared memory, where that is allowed)
-    const int cap_elems = backward ? (elem_bytes == 2 ? 20 : 16) : (wide_fwd ? 56 : 32);
-    const int min_vb = backward ? (elem_bytes == 4 ? 8 : 4) : (elem_bytes == 4 ? 16 : 8);
-    for (int cvb = 16; cvb >= min_vb && !tail; cvb >>= 1) {
-      const int cvec = cvb / elem_bytes;
-      if (7 * cvec > cap_elems || cols % cvec != 0) continue;
+    struct Cand {
+      int k, vb;
+    };
+    static const Cand kFwd32[] = {{8, 16}, {7, 16}, {6, 16}, {5, 16}, {4, 16}, {3, 16}};
+    static const Cand kFwd16Wide[] = {{7, 16}, {6, 16}, {5, 16}, {4, 16}, {7, 8}, {3, 16}};
+    static const Cand kFwd16[] = {{4, 16}, {7, 8}, {3, 16}};
+    static const Cand kBwd32[] = {{7, 8}, {4, 16}, {3, 16}, {5, 8}};
+    static const Cand kBwd16[] = {{7, 4}, {5, 8}, {4, 8}, {3, 8}};
+    const Cand* cand = backward ? (elem_bytes == 4 ? kBwd32 : kBwd16) : (elem_bytes == 4 ? kFwd32 : (wide_fwd ? kFwd16Wide : kFwd16));
+    const int ncand = backward ? 4 : (elem_bytes == 4 ? 6 : (wide_fwd ? 6 : 3));
+    for (int c = 0; c < ncand && !tail; ++c) {
+      const int ck = cand[c].k, cvb = cand[c].vb, cvec = cvb / elem_bytes;
+      if (cols % cvec != 0) continue;
       const int cnv = cols / cvec;
-      const int t = next_pow2i((cnv + 6) / 7);
-      if (t < (backward ? 64 : 32) || t > 512 || (int64_t)6 * t >= cnv) continue;
+      const int t = next_pow2i((cnv + ck - 1) / ck);
+      if (t < (backward ? 64 : 32) || t > 512 || (int64_t)(ck - 1) * t >= cnv) continue;
       const int thr = t > cta_threads ? t : cta_threads;
       if (rows % (thr / t) != 0) continue;
-      K = 7;
+      K = ck;
       tpr = t;
       vb = cvb;
       tail = true;
@@ -298,25 +314,31 @@ void set_pair_slots(int n) {
 // half row, one row per tile) with `pair` set and the grid counted in CTAs (two per row slot).
 PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
   PipePlan P = plan_pipeline(true, rows, cols, es, with_dres ? 3 : 2);
-  // 16-bit rows of 16384 columns: one CTA per row, two passes over the staged row
-  // (fln_pipeline_bwd_wide.cu); two stages of dy + x and the dbeta accumulators behind them
-  if (!P.ok && !with_dres && es == 2 && (cols == 16384 || cols == 14336) && rows > 0 &&
+  // 16-bit rows beyond the one-pass kernel's columns per thread, up to 16384 columns: one CTA
+  // per row, two passes over the staged row (fln_pipeline_bwd_wide.cu); stages of dy + x and
+  // the dbeta accumulators behind them.  16384 and 14336 columns divide exactly (4 vectors of
+  // 16 bytes, 7 of 8 bytes per thread); other multiples of 8 columns get 3 or 4 vectors of 16
+  // bytes of which the last is ragged.
+  if (!P.ok && !with_dres && es == 2 && cols > 8192 && cols <= 16384 && cols % 8 == 0 && cols != 12288 && rows > 0 &&
       g_path_override.load(std::memory_order_relaxed) != 3) {
     PipePlan W;
     memset(&W, 0, sizeof(W));
     W.ok = true;
     W.wide = true;
-    W.vb = cols == 16384 ? 16 : 8;
-    W.K = cols == 16384 ? 4 : 7;
+    W.vb = cols == 14336 ? 8 : 16;
+    W.K = cols == 14336 ? 7 : (cols > 12288 ? 4 : 3);
+    W.tail = cols != 14336 && cols != W.K * 4096;
     W.threads = 512;
     W.g.R = 1;
     W.g.tpr = 512;
     W.g.log2_tpr = 9;
-    W.g.S = 2;
     W.g.row_bytes = (uint32_t)cols * 2;
     W.g.second_off = W.g.row_bytes;
     W.g.stage_stride = 2 * W.g.row_bytes;
-    W.smem = (size_t)kSmemHeader + 2 * (size_t)W.g.stage_stride + (size_t)(cols / 1024) * 512 * sizeof(float2);
+    // dbeta accumulators: one float2 per thread and column pair
+    const size_t accb = (size_t)W.K * (W.vb / 4) * 512 * sizeof(float2);
+    W.g.S = W.K == 3 ? 3 : 2;
+    W.smem = (size_t)kSmemHeader + (size_t)W.g.S * W.g.stage_stride + accb;
     const int64_t cap = usable_sms();
     W.grid = (int)(rows < cap ? rows : cap);
     return W;
@@ -412,8 +434,9 @@ extern "C" int fln_planner_selftest(void) {
             if (P.full) ok = ok && (int64_t)P.K * P.g.tpr * vec == cols && rows % P.g.R == 0;
             // odd K or short vectors exist only as branch-free instantiations
             if ((P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 6 || P.K == 7) && !P.full && !P.tail) ok = false;
-            // a ragged last vector: K = 7, vectors 0 .. 5 whole, rows fill the CTA
-            if (P.tail) ok = ok && P.K == 7 && !P.full && (int64_t)6 * P.g.tpr < cols / vec && rows % P.g.R == 0;
+            // a ragged last vector: vectors 0 .. K - 2 whole, rows fill the CTA
+            if (P.tail)
+              ok = ok && P.K >= 3 && P.K <= 8 && !P.full && (int64_t)(P.K - 1) * P.g.tpr < cols / vec && rows % P.g.R == 0;
             if (!ok) ++bad;
           }
   return bad;

@@ -88,10 +88,11 @@ int launch_bwd_pipeline(int kind, int dtype, const BwdParams& p0, cudaStream_t s
     p.sync = nullptr;
   }
   // plans served by the other translation units
-  const bool shared_row = P.pair || P.tail;
+  const bool shared_row = P.pair;
   const bool odd = P.vb != 16 || P.K == 3 || P.K == 5 || P.K == 7;
 #define FLN_RUN(T)                                                                          \
   (P.wide ? bwd_pipe_wide_any(kind, dtype, p, P, st) :                                      \
+   P.tail ? bwd_pipe_tail_any(kind, dtype, p, P, st) :                                      \
    shared_row ? bwd_pipe_pair_any(kind, dtype, p, P, st)                                    \
               : (odd ? bwd_pipe_odd_any(kind, dtype, p, P, st)                              \
                      : (kind == FLN_LAYERNORM ? bwd_pipe_k<T, FLN_LAYERNORM>(p, P, st)      \

@@ -514,5 +514,6 @@ static int launch_bwd_kernel(KernelT kern, const BwdParams& p, const PipePlan& P
 int bwd_pipe_odd_any(int kind, int dtype, const BwdParams& p, const PipePlan& P, cudaStream_t st);
 int bwd_pipe_pair_any(int kind, int dtype, const BwdParams& p, const PipePlan& P, cudaStream_t st);
 int bwd_pipe_wide_any(int kind, int dtype, const BwdParams& p, const PipePlan& P, cudaStream_t st);
+int bwd_pipe_tail_any(int kind, int dtype, const BwdParams& p, const PipePlan& P, cudaStream_t st);
 
 }  // namespace fln

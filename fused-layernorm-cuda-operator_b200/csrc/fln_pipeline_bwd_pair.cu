@@ -1,5 +1,4 @@
-// Pipelined backward: rows shared by the two CTAs of a thread-block cluster, and rows whose last
-// vector is ragged.
+// Pipelined backward: rows shared by the two CTAs of a thread-block cluster.
 #include "fln_pipeline_bwd_kernel.cuh"
 
 namespace fln {
@@ -19,23 +18,6 @@ static int bwd_pipe_pair(const BwdParams& p, const PipePlan& P, cudaStream_t st)
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
-// rows whose last vector is ragged (plan_pipeline's `tail` plans): K = 7 vectors of 4 bytes
-// (16-bit types) or 8 bytes (fp32), 14 columns per thread
-template <typename T, int KIND>
-static int bwd_pipe_tail(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
-  constexpr int VB = sizeof(T) == 2 ? 4 : 8;
-  if (P.K != 7 || P.vb != VB || P.threads != 512 || p.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
-  const bool fuse = p.sync != nullptr;
-#define FLN_TAIL_LT(L)                                                                                                  \
-  if (P.g.tpr == (1 << L)) {                                                                                            \
-    if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, 7, KIND, true, true, false, VB, L, false, true>, p, P, st); \
-    return launch_bwd_kernel(norm_bwd_pipe_kernel<T, 7, KIND, true, false, false, VB, L, false, true>, p, P, st);       \
-  }
-  FLN_TAIL_LT(6) FLN_TAIL_LT(7) FLN_TAIL_LT(8) FLN_TAIL_LT(9)
-#undef FLN_TAIL_LT
-  return FLN_PIPE_NOT_APPLICABLE;
-}
-
 #define FLN_BY_TYPE(FN)                                                                               \
   if (kind == FLN_LAYERNORM) {                                                                        \
     if (dtype == FLN_F32) return FN<float, FLN_LAYERNORM>(p, P, st);                                  \
@@ -49,9 +31,6 @@ static int bwd_pipe_tail(const BwdParams& p, const PipePlan& P, cudaStream_t st)
 int bwd_pipe_pair_any(int kind, int dtype, const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   if (P.pair) {
     FLN_BY_TYPE(bwd_pipe_pair)
-  }
-  if (P.tail) {
-    FLN_BY_TYPE(bwd_pipe_tail)
   }
   return FLN_PIPE_NOT_APPLICABLE;
 }

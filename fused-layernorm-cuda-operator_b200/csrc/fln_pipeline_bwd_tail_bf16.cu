@@ -1,0 +1,10 @@
+// Ragged-last-vector backward, bf16 rows.
+#include "fln_pipeline_bwd_tail.cuh"
+
+namespace fln {
+
+int bwd_pipe_tail_bf16(int kind, const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  return bwd_tail_typed<__nv_bfloat16>(kind, p, P, st);
+}
+
+}  // namespace fln

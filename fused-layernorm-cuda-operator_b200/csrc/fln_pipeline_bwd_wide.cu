@@ -1,5 +1,5 @@
-// Pipelined backward for 16-bit rows of 16384 (and 14336) columns: one 512-thread CTA per row, 32
-// (28) columns per thread, in two passes over the staged row.
+// Pipelined backward for 16-bit rows of 10248 .. 16384 columns: one 512-thread CTA per row, up to
+// 32 columns per thread, in two passes over the staged row.
 //
 // 32 columns per thread do not fit the registers of the one-pass kernel (the row as floats, gamma
 // and two accumulators per column), and a row shared by a cluster pair pays half a microsecond
@@ -10,22 +10,32 @@
 // dgamma accumulators (32); the dbeta accumulators sit in shared memory behind the stages
 // (conflict-free float2 per thread and column pair).  Two CTA barriers per row: the reduction,
 // and the release of the stage after pass 2.
+//
+// Rows of 16384 and 14336 columns divide exactly (4 vectors of 16 bytes, 7 of 8 bytes per
+// thread).  Any other row length that is a multiple of 8 runs the TAIL form: 3 or 4 vectors of 16
+// bytes per thread of which only the last is tested against the end of the row (11008 = 43 *
+// 256, 12800, 13824 = 27 * 512 columns ...).
 #include "fln_pipeline_bwd_kernel.cuh"
 
 namespace fln {
 
-// rows of K * (VB / 2) * 512 columns: (K, VB) = (4, 16) -> 16384, (7, 8) -> 14336
-template <typename T, int KIND, int K, int VB>
+// rows of K * (VB / 2) * 512 columns: (K, VB) = (4, 16) -> 16384, (7, 8) -> 14336; TAIL: rows of
+// more than (K - 1) * (VB / 2) * 512 and fewer than K * (VB / 2) * 512 columns
+template <typename T, int KIND, int K, int VB, bool TAIL = false>
 __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / 2, V2 = VEC / 2, NR = KIND == FLN_LAYERNORM ? 2 : 1;
-  constexpr int cols = K * VEC * 512;
-  constexpr uint32_t row_bytes = cols * 2, stage_stride = 2 * row_bytes, k_off = 512 * VB;
+  const int cols = TAIL ? p.cols : K * VEC * 512;
+  const uint32_t row_bytes = (uint32_t)cols * 2u, stage_stride = 2u * row_bytes;
+  constexpr uint32_t k_off = 512 * VB;
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   float* s_red = reinterpret_cast<float*>(smem + 256);
   unsigned char* stages = smem + kSmemHeader;
   const int tid = threadIdx.x;
   const int S = g.S;
+  // this thread's last vector lies in the row (the others do for every thread)
+  const bool last_ok = !TAIL || tid + (K - 1) * 512 < p.nv;
+#define FLN_IN_ROW(k) (!TAIL || (k) < K - 1 || last_ok)
   float2* s_accb = reinterpret_cast<float2*>(stages + (size_t)S * stage_stride) + tid;  // [K * V2][512]
 
   const int my_tiles = my_tile_count(p.rows);
@@ -56,7 +66,7 @@ __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p
   for (int k = 0; k < K; ++k) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) gp[k].e[e] = Cvt<T>::from_f(1.f);
-    if (p.gamma != nullptr) gp[k] = ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + (int64_t)(tid + k * 512) * VEC);
+    if (p.gamma != nullptr && FLN_IN_ROW(k)) gp[k] = ld_param<T, VEC>(reinterpret_cast<const T*>(p.gamma) + (int64_t)(tid + k * 512) * VEC);
 #pragma unroll
     for (int e = 0; e < V2; ++e) {
       acc_g[k][e] = f2(0.f);
@@ -89,6 +99,7 @@ __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p
     float2 r0 = f2(0.f), r1 = f2(0.f);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      if (!FLN_IN_ROW(k)) continue;
       float2 dyf[V2], xh[V2], gm[V2];
       unpack2<T, VEC>(stage_vec<T, VEC>(st + k * k_off), dyf);
       unpack2<T, VEC>(stage_vec<T, VEC>(st + row_bytes + k * k_off), xh);
@@ -118,6 +129,7 @@ __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p
     T* __restrict__ dxr = reinterpret_cast<T*>(p.dx) + row * (int64_t)cols + (int64_t)tid * VEC;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      if (!FLN_IN_ROW(k)) continue;
       float2 dyf[V2], xh[V2], gm[V2];
       unpack2<T, VEC>(stage_vec<T, VEC>(st + k * k_off), dyf);
       unpack2<T, VEC>(stage_vec<T, VEC>(st + row_bytes + k * k_off), xh);
@@ -151,6 +163,7 @@ __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p
     float* __restrict__ pg = p.partials + (int64_t)blockIdx.x * (int64_t)(NR * cols);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
+      if (!FLN_IN_ROW(k)) continue;
       const int64_t c0 = (int64_t)(tid + k * 512) * VEC;
 #pragma unroll
       for (int e = 0; e < V2; e += 2) {  // V2 is 4 or 2
@@ -163,11 +176,12 @@ __global__ void __launch_bounds__(512) norm_bwd_twopass_kernel(const BwdParams p
       }
     }
   }
+#undef FLN_IN_ROW
 }
 
-template <typename T, int KIND, int K, int VB>
+template <typename T, int KIND, int K, int VB, bool TAIL = false>
 static int launch_twopass(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
-  auto kern = norm_bwd_twopass_kernel<T, KIND, K, VB>;
+  auto kern = norm_bwd_twopass_kernel<T, KIND, K, VB, TAIL>;
   if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
   kern<<<P.grid, 512, P.smem, st>>>(p, P.g);
   FLN_CHECK_LAUNCH();
@@ -176,6 +190,16 @@ static int launch_twopass(const BwdParams& p, const PipePlan& P, cudaStream_t st
 
 template <typename T>
 static int twopass_typed(int kind, const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (P.tail) {
+    if (P.vb != 16 || p.cols % 8 != 0 || p.cols <= (P.K - 1) * 4096 || p.cols >= P.K * 4096) return FLN_PIPE_NOT_APPLICABLE;
+    if (P.K == 3)
+      return kind == FLN_LAYERNORM ? launch_twopass<T, FLN_LAYERNORM, 3, 16, true>(p, P, st)
+                                   : launch_twopass<T, FLN_RMSNORM, 3, 16, true>(p, P, st);
+    if (P.K == 4)
+      return kind == FLN_LAYERNORM ? launch_twopass<T, FLN_LAYERNORM, 4, 16, true>(p, P, st)
+                                   : launch_twopass<T, FLN_RMSNORM, 4, 16, true>(p, P, st);
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
   if (P.K == 4 && P.vb == 16 && p.cols == 16384)
     return kind == FLN_LAYERNORM ? launch_twopass<T, FLN_LAYERNORM, 4, 16>(p, P, st)
                                  : launch_twopass<T, FLN_RMSNORM, 4, 16>(p, P, st);

@@ -39,41 +39,13 @@ static int fwd_pipe_odd(const FwdParams& p, const PipePlan& P, cudaStream_t st) 
   }
 }
 
-// rows whose last vector is ragged (plan_pipeline's `tail` plans): K = 7 vectors of 8 bytes
-// (16-bit types) or 16 bytes (fp32); plain forward only
+// rows whose last vector is ragged (plan_pipeline's `tail` plans): instantiated in
+// fln_pipeline_fwd_tail.cu; plain forward only
 template <typename TI, typename TO, int KIND, int ACT>
 static int fwd_pipe_tail(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   if constexpr (ACT == FLN_ACT_NONE && std::is_same<TI, TO>::value) {
-    constexpr int VB = sizeof(TI) == 2 ? 8 : 16;
-    const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
-    if (P.K != 7 || P.threads != nt) return FLN_PIPE_NOT_APPLICABLE;
-    // 16-bit types, 16-byte vectors: 56 elements per thread, gamma / beta in shared memory
-    if constexpr (sizeof(TI) == 2) {
-      if (P.vb == 16) {
-#define FLN_GO7(LTT)                                                         \
-  if (P.g.tpr == (1 << LTT)) {                                               \
-    auto kern = norm_fwd_pipe_kernel<TI, TO, 7, KIND, ACT, 7, 16, LTT>;      \
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;             \
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                         \
-    FLN_CHECK_LAUNCH();                                                      \
-    return FLN_OK;                                                           \
-  }
-        FLN_GO7(5) FLN_GO7(6) FLN_GO7(7) FLN_GO7(8) FLN_GO7(9)
-#undef FLN_GO7
-        return FLN_PIPE_NOT_APPLICABLE;
-      }
-    }
-    if (P.vb != VB) return FLN_PIPE_NOT_APPLICABLE;
-#define FLN_GO(LTT)                                                          \
-  if (P.g.tpr == (1 << LTT)) {                                               \
-    auto kern = norm_fwd_pipe_kernel<TI, TO, 7, KIND, ACT, 5, VB, LTT>;      \
-    if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;             \
-    kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);                         \
-    FLN_CHECK_LAUNCH();                                                      \
-    return FLN_OK;                                                           \
-  }
-    FLN_GO(5) FLN_GO(6) FLN_GO(7) FLN_GO(8) FLN_GO(9)
-#undef FLN_GO
+    constexpr int dtype = std::is_same<TI, float>::value ? FLN_F32 : (std::is_same<TI, __half>::value ? FLN_F16 : FLN_BF16);
+    return fwd_pipe_tail_any(KIND, dtype, p, P, st);
   }
   return FLN_PIPE_NOT_APPLICABLE;
 }

@@ -480,5 +480,7 @@ __global__ void __launch_bounds__(512, MODE == 6 ? 2 : 1) norm_fwd_pipe_kernel(c
 // what every launch of the kernel needs besides the caller's pointers: the tile counters, the
 // wait limit, the status and test-hook words.  false if the device words cannot be had.
 bool fwd_pipe_prepare(FwdParams* p);
+// the ragged-last-vector instantiations (fln_pipeline_fwd_tail.cu)
+int fwd_pipe_tail_any(int kind, int dtype, const FwdParams& p, const PipePlan& P, cudaStream_t st);
 
 }  // namespace fln

@@ -1,0 +1,17 @@
+// Ragged-last-vector forward, fp32 rows, and the dispatch by type.
+#include "fln_pipeline_fwd_tail.cuh"
+
+namespace fln {
+
+int fwd_pipe_tail_f32(int kind, const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  return fwd_tail_typed<float>(kind, p, P, st);
+}
+
+int fwd_pipe_tail_any(int kind, int dtype, const FwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (dtype == FLN_F32) return fwd_pipe_tail_f32(kind, p, P, st);
+  if (dtype == FLN_BF16) return fwd_pipe_tail_bf16(kind, p, P, st);
+  if (dtype == FLN_F16) return fwd_pipe_tail_f16(kind, p, P, st);
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
+}  // namespace fln

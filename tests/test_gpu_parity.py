@@ -679,16 +679,21 @@ def test_rows_shared_by_the_two_ctas_of_a_cluster(path_override, shape, dtype, k
 
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype,shape", [(BF16, (1200, 16384)), (F16, (700, 16384)), (BF16, (600, 14336)),
-                                         (F16, (900, 14336))])
+                                         (F16, (900, 14336)), (BF16, (700, 11008)), (F16, (650, 13824)),
+                                         (BF16, (600, 12800)), (F16, (610, 10248)), (BF16, (620, 12296)),
+                                         (BF16, (630, 16376)), (F16, (640, 12280))])
 def test_long_16bit_rows_in_two_passes(path_override, shape, dtype, kind):
-    """16-bit rows of 16384 / 14336 columns: one CTA per row, 32 / 28 columns per thread, the row
-    sums from a first pass over the staged row, dx and the column sums from a second.  The plan
-    must be that one, the results the checker's, two runs bit-identical."""
+    """16-bit rows of 10248 .. 16384 columns: one CTA per row, up to 32 columns per thread, the row
+    sums from a first pass over the staged row, dx and the column sums from a second; rows other
+    than 16384 / 14336 columns with a ragged last vector per thread (down to a single vector of
+    the row in it: 12296 columns).  The plan must be that one, the results the checker's, two runs
+    bit-identical."""
     path_override(2)
     rows, cols = shape
     d = capi.describe_launch(True, rows, cols, dtype)
-    assert d["pipelined"] == 1 and d["threads_per_row"] == 512 and d["stages"] == 2
-    assert d["vecs_per_thread"] * (d["vector_bytes"] // 2) * 512 == cols
+    assert d["pipelined"] == 1 and d["threads_per_row"] == 512 and d["rows_per_cta"] == 1
+    k, nv = d["vecs_per_thread"], cols // (d["vector_bytes"] // 2)
+    assert (k - 1) * 512 < nv <= k * 512 and d["stages"] == (3 if k == 3 else 2)
     x, gamma, beta, dy, _ = U.make_inputs(_seed(rows, cols) + 19, rows, cols, dtype)
     f = O.norm_forward(x, gamma, None if kind == "rmsnorm" else beta, None, kind)
     got = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind)
@@ -765,21 +770,25 @@ def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape,
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype", [BF16, F32, F16])
 @pytest.mark.parametrize("shape", [(4096, 1600), (1024, 1664), (2048, 800), (512, 3200), (256, 6400), (128, 12800),
-                                   (4098, 1600)])
+                                   (4098, 1600), (1024, 4608), (256, 9216), (768, 3840), (512, 5376), (256, 11008),
+                                   (2048, 1152), (1024, 2304), (512, 2880), (256, 7680), (128, 13824), (1024, 1000)])
 def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
-    """Row lengths that fit no exact plan (1600 = 25 * 64): seven vectors per thread of which only
-    the last is ragged.  The plan must be that one where the rows fill the CTA's row slots (4098
-    rows do not: the padded plan runs), results the checker's, forward with and without a
-    residual, backward with and without the incoming residual-stream gradient (the latter on
-    the padded plan), two backward runs bit-identical."""
+    """Row lengths that fit no exact plan (1600 = 25 * 64, 4608 = 9 * 512): K vectors per thread of
+    which only the last is ragged.  The plan must be such a one where the rows fill the CTA's row
+    slots (4098 rows do not: the padded plan runs) and the row is within the backward's columns
+    per thread, results the checker's, forward with and without a residual, backward with and
+    without the incoming residual-stream gradient (the latter on the padded plan), two backward
+    runs bit-identical."""
     path_override(2)
     rows, cols = shape
     for backward in (False, True):
         d = capi.describe_launch(backward, rows, cols, dtype)
-        if rows != 4098 and (not backward or cols <= 7168):  # 14 columns for each of up to 512 threads
-            assert d["pipelined"] == 1 and d["vecs_per_thread"] == 7
+        # backward: up to 20 (16-bit) or 16 (fp32) columns for each of up to 512 threads
+        if rows != 4098 and (not backward or cols <= (8192 if dtype == F32 else 10240)):
+            k, t = d["vecs_per_thread"], d["threads_per_row"]
             nv = cols // (d["vector_bytes"] // dtype.itemsize)
-            assert 6 * d["threads_per_row"] < nv <= 7 * d["threads_per_row"]
+            assert d["pipelined"] == 1 and 3 <= k <= 8
+            assert (k - 1) * t < nv < k * t
     x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 17, rows, cols, dtype, residual=True)
     if kind == "rmsnorm":
         beta = None
