@@ -165,8 +165,16 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   //             16-bit  16 B x 7 .. 5, gamma / beta in shared memory (56 .. 40), 16 B x 4, 8 B x 7, 16 B x 3
   //   backward  fp32    8 B x 7, 16 B x 4, 3, 8 B x 5          (10 .. 16 columns)
   //             16-bit  4 B x 7, 8 B x 5, 4, 3                 (12 .. 20 columns)
+  // 16-bit forward rows of 14336 columns divide into 7 x 8 bytes x 512 threads, one CTA per SM;
+  // four 16-byte vectors with the last one ragged run two CTAs per SM (5829 against 5200 GB/s)
+  // and rows of 7 x 8 bytes on fewer threads are served better by the ragged kernel's seven 16-byte
+  // vectors on half the threads with gamma / beta in shared memory, although no vector is
+  // ragged (7168 columns: 6237 -> 6492 GB/s as measured on 7160)
+  const bool prefer_ragged = !backward && elem_bytes == 2 && K == 7 && vb == 8 &&
+                             ((tensors == 1 && tpr == 512) || (wide_fwd && tpr >= 64));
   bool tail = false;
-  if (allow_tail && fK == 0 && tensors <= 2 && (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes))) {
+  if (allow_tail && fK == 0 && tensors <= 2 &&
+      (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes) || prefer_ragged)) {
     struct Cand {
       int k, vb;
     };
@@ -212,8 +220,9 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // registers each) with gamma / beta fetched per row (plain forward only): 5420 -> 5884 GB/s.
   // With 5 or 6 vectors per thread the same form was slower than one CTA per SM (bf16 20480:
   // 5072 against 5831 GB/s, fp32 12288: 5108 against 5727; fp32 10240 unchanged).
-  const bool pgl = !backward && allow_tail && !tail && threads == 512 && tpr == 512 && tensors == 1 && vb == 16 &&
-                   elem_bytes == 2 && K == 4 && (int64_t)K * tpr == cols / (vb / elem_bytes) &&
+  // The same with a ragged last vector (12296 .. 16376 columns).
+  const bool pgl = !backward && allow_tail && threads == 512 && tpr == 512 && tensors == 1 && vb == 16 &&
+                   elem_bytes == 2 && K == 4 && (tail || (int64_t)K * tpr == cols / (vb / elem_bytes)) &&
                    (size_t)kSmemHeader + 2 * (size_t)stage <= 100 * 1024;
   const int ctas_per_sm = (threads >= 512 && !pgl) ? 1 : 2;
   const size_t budget = (size_t)(200 * 1024) / ctas_per_sm;
@@ -228,8 +237,8 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   if (fS >= 2) S = fS;
   if (S > S_fit) S = S_fit;
   P.ok = true;
-  P.full = (tpr >= 32 || (!backward && K == 6 && tpr == 16)) && (int64_t)K * tpr == cols / (vb / elem_bytes) &&
-           rows % R == 0;
+  P.full = !tail && (tpr >= 32 || (!backward && K == 6 && tpr == 16)) && (int64_t)K * tpr == cols / (vb / elem_bytes) &&
+           rows % R == 0;  // a `tail` plan runs its own instantiations even where its last vector happens to be whole
   P.tail = tail;
   P.pgl = pgl;
   P.vb = vb;

@@ -58,20 +58,20 @@ template <typename TI, typename TO, int K, int KIND, int ACT, int MODE, int VB =
 // living in registers, and the kernel held to 64 registers: two 512-thread CTAs per SM for rows
 // that need 512 threads (one CTA of 512 threads per SM walks its rows in lockstep at a quarter
 // of the warp slots).
-__global__ void __launch_bounds__(512, MODE == 6 ? 2 : 1) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
+__global__ void __launch_bounds__(512, (MODE == 6 || MODE == 8) ? 2 : 1) norm_fwd_pipe_kernel(const FwdParams p, const PipeGeom g) {
   constexpr int VEC = VB / sizeof(TI);  // a multiple of 4 (the statistics run four chains)
   constexpr int V2 = VEC / 2;
   constexpr bool FULL = MODE >= 1;
   constexpr bool PSM = MODE == 4 || MODE == 7;  // MODE 7: the ragged last vector and the parameters in shared memory
-  constexpr bool PGL = MODE == 6;
-  constexpr bool TAIL = MODE == 5 || MODE == 7;
+  constexpr bool PGL = MODE == 6 || MODE == 8;  // MODE 8: the same with a ragged last vector
+  constexpr bool TAIL = MODE == 5 || MODE == 7 || MODE == 8;
   constexpr bool Q8 = QM > 0;
   static_assert(QM == 0 || (VEC == 8 && MODE == 1), "quantized outputs: 16-bit input, 16-byte vectors, exact rows");
   static_assert(!DROP || (VEC == 8 && MODE == 1), "dropout: 16-bit input, 16-byte vectors, exact rows");
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   constexpr int NT = LTC > 8 ? (1 << LTC) : 256;  // threads per CTA of the compile-time geometry
-  static_assert(!CT || MODE == 1 || (MODE >= 4 && MODE <= 7), "compile-time geometry is for the FULL kernels");
+  static_assert(!CT || MODE == 1 || (MODE >= 4 && MODE <= 8), "compile-time geometry is for the FULL kernels");
   static_assert(!TAIL || CT, "the ragged-last-vector kernel has its split at compile time");
 // vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
 #define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))

@@ -9,7 +9,8 @@
 // it.  Plain forward only (no activation, output in the input's type).
 //   fp32    16-byte vectors x 3 .. 8 (12 .. 32 elements per thread)
 //   16-bit  16-byte vectors x 5 .. 7 with gamma / beta in shared memory (40 .. 56 elements),
-//           16-byte vectors x 3, 4 and 8-byte vectors x 7 with them in registers
+//           16-byte vectors x 3, 4 and 8-byte vectors x 7 with them in registers; rows of 512
+//           threads x 4 vectors with them fetched per row, two CTAs per SM
 #pragma once
 #include "fln_pipeline_fwd_kernel.cuh"
 
@@ -34,6 +35,19 @@ template <typename T, int KIND>
 static int fwd_tail_kind(const FwdParams& p, const PipePlan& P, cudaStream_t st) {
   const int nt = P.g.tpr > 256 ? P.g.tpr : 256;
   if (!P.tail || P.threads != nt) return FLN_PIPE_NOT_APPLICABLE;
+  // 16-bit rows of 512 threads, two CTAs per SM, gamma / beta fetched per row (`pgl` plans)
+  if (P.pgl) {
+    if constexpr (sizeof(T) == 2) {
+      if (P.K == 4 && P.vb == 16 && P.g.tpr == 512) {
+        auto kern = norm_fwd_pipe_kernel<T, T, 4, KIND, FLN_ACT_NONE, 8, 16, 9>;
+        if (set_smem(kern, P.smem) != FLN_OK) return FLN_ERR_LAUNCH;
+        kern<<<P.grid, P.threads, P.smem, st>>>(p, P.g);
+        FLN_CHECK_LAUNCH();
+        return FLN_OK;
+      }
+    }
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
 #define FLN_TAIL(KK, VBB, MODE) \
   if (P.K == KK && P.vb == VBB) return fwd_tail_go<T, KIND, KK, MODE, VBB>(p, P, st);
   if constexpr (sizeof(T) == 4) {
