@@ -354,7 +354,9 @@ PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
   }
   if (!P.ok && !with_dres && cols % 2 == 0 && g_path_override.load(std::memory_order_relaxed) != 3) {
     PipePlan H = plan_pipeline(true, rows, cols / 2, es, 2);
-    if (H.ok && H.full && !H.bsm && H.threads == 512 && H.g.tpr == 512 && H.g.R == 1 && H.K * (H.vb / es) <= 20) {
+    // (a ragged half row: its first column must sit on a 16-byte boundary for the bulk copies)
+    if (H.ok && (H.full || (H.tail && cols % (32 / es) == 0)) && !H.bsm && H.threads == 512 && H.g.tpr == 512 &&
+        H.g.R == 1 && H.K * (H.vb / es) <= 20) {
       H.pair = true;
       const int64_t slots = pair_slots();
       H.grid = (int)(2 * (rows < slots ? rows : slots));

@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   static_assert(!CT || FULL, "compile-time geometry is for the FULL kernel");
-  static_assert(!TAIL || (CT && !PAIR && !DRES), "the ragged-last-vector kernel: split at compile time, plain stage 1");
+  static_assert(!TAIL || (CT && !DRES), "the ragged-last-vector kernel: split at compile time, plain stage 1");
 // vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
 #define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
   static_assert(!PAIR || (LT == 9 && !FUSE && !DRES), "a shared row: 512 threads per half row, plain stage 1");
@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   const int tpr = CT ? (1 << LTC) : g.tpr;
   const int log2_tpr = CT ? LTC : g.log2_tpr;
   const int R = CT ? (512 >> LTC) : g.R;
-  const int cols = (CT && !TAIL) ? ((K * VEC) << LTC) : p.cols;
+  // (a shared ragged row: this CTA's half of it)
+  const int cols = (CT && !TAIL) ? ((K * VEC) << LTC) : (PAIR ? p.cols >> 1 : p.cols);
   const uint32_t row_bytes = (CT && !TAIL) ? (uint32_t)((K * VB) << LTC) : g.row_bytes;
   const uint32_t second_off = CT ? row_bytes * (uint32_t)R : g.second_off;
   const uint32_t stage_stride = CT ? second_off * (uint32_t)NPROD : g.stage_stride;
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int iv = lane_r + k * tpr;
-    vok[k] = FLN_WHOLE(k) ? true : iv < p.nv;
+    vok[k] = FLN_WHOLE(k) ? true : iv < (PAIR ? p.nv >> 1 : p.nv);
 #pragma unroll
     for (int e = 0; e < V2; ++e) {
       acc_g[k][e] = f2(0.f);

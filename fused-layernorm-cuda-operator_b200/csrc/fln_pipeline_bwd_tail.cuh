@@ -8,7 +8,8 @@
 //   fp32    16-byte vectors x 3, 4 and 8-byte vectors x 5, 7   (10 .. 16 columns)
 //   16-bit  8-byte vectors x 3, 4, 5 and 4-byte vectors x 7    (12 .. 20 columns)
 // With the column sums reduced by the kernel's own tail (cooperative launch) or left to a
-// second launch.
+// second launch.  Longer ragged rows are shared by the two CTAs of a cluster, each half row
+// planned the same way (fp32 9216, 11008, 13824 columns; 16-bit 18432).
 #pragma once
 #include "fln_pipeline_bwd_kernel.cuh"
 
@@ -27,11 +28,21 @@ static int bwd_tail_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
+// a ragged row shared by the two CTAs of a cluster: each half row on 512 threads
+template <typename T, int KIND, int KK, int VB>
+static int bwd_tail_pair_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if (P.g.tpr != 512 || p.sync != nullptr) return FLN_PIPE_NOT_APPLICABLE;
+  return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, false, false, VB, 9, true, true>, p, P, st);
+}
+
 template <typename T, int KIND>
 static int bwd_tail_kind(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   if (!P.tail || P.threads != 512 || p.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
-#define FLN_TAIL(KK, VBB) \
-  if (P.K == KK && P.vb == VBB) return bwd_tail_go<T, KIND, KK, VBB>(p, P, st);
+#define FLN_TAIL(KK, VBB)         \
+  if (P.K == KK && P.vb == VBB) { \
+    if (P.pair) return bwd_tail_pair_go<T, KIND, KK, VBB>(p, P, st); \
+    return bwd_tail_go<T, KIND, KK, VBB>(p, P, st);                  \
+  }
   if constexpr (sizeof(T) == 4) {
     FLN_TAIL(4, 16) FLN_TAIL(3, 16) FLN_TAIL(7, 8) FLN_TAIL(5, 8)
   } else {
