@@ -164,7 +164,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   //   forward   fp32    16 B x 8 .. 3                          (32 .. 12 elements)
   //             16-bit  16 B x 7 .. 5, gamma / beta in shared memory (56 .. 40), 16 B x 4, 8 B x 7, 16 B x 3
   //   backward  fp32    8 B x 7, 16 B x 4, 3, 8 B x 5          (10 .. 16 columns)
-  //             16-bit  4 B x 7, 8 B x 5, 4, 3                 (12 .. 20 columns)
+  //             16-bit  4 B x 7, 8 B x 5, 4, 16 B x 3, 8 B x 3     (12 .. 24 columns)
   // 16-bit forward rows of 14336 columns divide into 7 x 8 bytes x 512 threads, one CTA per SM;
   // four 16-byte vectors with the last one ragged run two CTAs per SM (5829 against 5200 GB/s)
   // and rows of 7 x 8 bytes on fewer threads are served better by the ragged kernel's seven 16-byte
@@ -182,15 +182,18 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
     static const Cand kFwd16Wide[] = {{7, 16}, {6, 16}, {5, 16}, {4, 16}, {7, 8}, {3, 16}};
     static const Cand kFwd16[] = {{4, 16}, {7, 8}, {3, 16}};
     static const Cand kBwd32[] = {{7, 8}, {4, 16}, {3, 16}, {5, 8}};
-    static const Cand kBwd16[] = {{7, 4}, {5, 8}, {4, 8}, {3, 8}};
+    static const Cand kBwd16[] = {{7, 4}, {5, 8}, {4, 8}, {3, 16}, {3, 8}};
     const Cand* cand = backward ? (elem_bytes == 4 ? kBwd32 : kBwd16) : (elem_bytes == 4 ? kFwd32 : (wide_fwd ? kFwd16Wide : kFwd16));
-    const int ncand = backward ? 4 : (elem_bytes == 4 ? 6 : (wide_fwd ? 6 : 3));
+    const int ncand = backward ? (elem_bytes == 4 ? 4 : 5) : (elem_bytes == 4 ? 6 : (wide_fwd ? 6 : 3));
     for (int c = 0; c < ncand && !tail; ++c) {
       const int ck = cand[c].k, cvb = cand[c].vb, cvec = cvb / elem_bytes;
       if (cols % cvec != 0) continue;
       const int cnv = cols / cvec;
       const int t = next_pow2i((cnv + ck - 1) / ck);
       if (t < (backward ? 64 : 32) || t > 512 || (int64_t)(ck - 1) * t >= cnv) continue;
+      // 24 columns per thread in the 16-bit backward: dbeta accumulators in shared memory, rows
+      // of up to 256 threads (longer rows run the two-pass kernel)
+      if (backward && elem_bytes == 2 && ck == 3 && cvb == 16 && (t > 256 || tensors != 2)) continue;
       const int thr = t > cta_threads ? t : cta_threads;
       if (rows % (thr / t) != 0) continue;
       K = ck;
@@ -256,7 +259,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   // 16-bit backward with 24 columns per thread: the dbeta accumulators (12 float2 per thread)
   // go behind the stages; the LayerNorm instantiation uses them, RMSNorm has none
   // (and the fp32 backward with 20 columns per thread, 10240 columns)
-  bool bsm = backward && vb == 16 && threads == 512 && tensors == 2 && P.full &&
+  bool bsm = backward && vb == 16 && threads == 512 && tensors == 2 && (P.full || (tail && elem_bytes == 2)) &&
              ((elem_bytes == 2 && K == 3) || (elem_bytes == 4 && K == 5));
   size_t bsm_bytes = bsm ? (size_t)(K * (16 / elem_bytes) / 2) * 512 * sizeof(float2) : 0;
   if ((size_t)kSmemHeader + (size_t)S * stage + bsm_bytes > 220 * 1024) {

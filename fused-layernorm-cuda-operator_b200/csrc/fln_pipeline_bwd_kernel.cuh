@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
 // vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
 #define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
   static_assert(!PAIR || (LT == 9 && !FUSE && !DRES), "a shared row: 512 threads per half row, plain stage 1");
-  static_assert(!BSM || (KIND == FLN_LAYERNORM && CT && !PAIR && !TAIL), "dbeta sums in shared memory: LayerNorm, 512 threads");
+  static_assert(!BSM || (KIND == FLN_LAYERNORM && CT && !PAIR), "dbeta sums in shared memory: LayerNorm, 512 threads");
   const int tpr = CT ? (1 << LTC) : g.tpr;
   const int log2_tpr = CT ? LTC : g.log2_tpr;
   const int R = CT ? (512 >> LTC) : g.R;

@@ -6,7 +6,8 @@
 // tested; rows fill the 512-thread CTA.  Columns per thread stay within what the one-pass
 // kernel holds in registers (the row as floats, gamma and two accumulators per column):
 //   fp32    16-byte vectors x 3, 4 and 8-byte vectors x 5, 7   (10 .. 16 columns)
-//   16-bit  8-byte vectors x 3, 4, 5 and 4-byte vectors x 7    (12 .. 20 columns)
+//   16-bit  8-byte vectors x 3, 4, 5 and 4-byte vectors x 7    (12 .. 20 columns),
+//           16-byte vectors x 3 with the dbeta accumulators in shared memory (24 columns)
 // With the column sums reduced by the kernel's own tail (cooperative launch) or left to a
 // second launch.  Longer ragged rows are shared by the two CTAs of a cluster, each half row
 // planned the same way (fp32 9216, 11008, 13824 columns; 16-bit 18432).
@@ -28,6 +29,25 @@ static int bwd_tail_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
+// 16-bit rows with three 16-byte vectors per thread (24 columns, up to 256 threads per row):
+// LayerNorm keeps its dbeta accumulators in shared memory (`bsm` plans), RMSNorm has none
+template <typename T, int KIND>
+static int bwd_tail_24_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2) {
+    const bool fuse = p.sync != nullptr;
+    if (KIND == FLN_LAYERNORM && !P.bsm) return FLN_PIPE_NOT_APPLICABLE;
+    constexpr bool BSM = KIND == FLN_LAYERNORM;
+#define FLN_TAIL_LT(L)                                                                                                        \
+  if (P.g.tpr == (1 << L)) {                                                                                                  \
+    if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, 3, KIND, true, true, false, 16, L, false, true, BSM>, p, P, st); \
+    return launch_bwd_kernel(norm_bwd_pipe_kernel<T, 3, KIND, true, false, false, 16, L, false, true, BSM>, p, P, st);        \
+  }
+    FLN_TAIL_LT(6) FLN_TAIL_LT(7) FLN_TAIL_LT(8)
+#undef FLN_TAIL_LT
+  }
+  return FLN_PIPE_NOT_APPLICABLE;
+}
+
 // a ragged row shared by the two CTAs of a cluster: each half row on 512 threads
 template <typename T, int KIND, int KK, int VB>
 static int bwd_tail_pair_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
@@ -46,6 +66,7 @@ static int bwd_tail_kind(const BwdParams& p, const PipePlan& P, cudaStream_t st)
   if constexpr (sizeof(T) == 4) {
     FLN_TAIL(4, 16) FLN_TAIL(3, 16) FLN_TAIL(7, 8) FLN_TAIL(5, 8)
   } else {
+    if (P.K == 3 && P.vb == 16 && !P.pair) return bwd_tail_24_go<T, KIND>(p, P, st);
     FLN_TAIL(5, 8) FLN_TAIL(4, 8) FLN_TAIL(3, 8) FLN_TAIL(7, 4)
   }
 #undef FLN_TAIL
