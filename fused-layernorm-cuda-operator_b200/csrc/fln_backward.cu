@@ -578,6 +578,50 @@ static int run_bwd(BwdParams p, void* dgamma, void* dbeta, float* dgb_f32, void*
   const bool want_params = defer || dgamma != nullptr || dbeta != nullptr || dgb_f32 != nullptr;
   // large aligned problems: persistent bulk-async pipeline for stage 1
   const int dt = sizeof(T) == 4 ? FLN_F32 : (std::is_same<T, __half>::value ? FLN_F16 : FLN_BF16);
+  // A row count that does not fill the fast plan's row slots: all but the last few rows through
+  // that plan (its column sums left as partial rows), those few through the register kernels
+  // (stage 1 only, their partial rows behind the pipeline's), then one column reduce over both.
+  const int64_t odd = aligned ? bwd_pipeline_odd_rows(dt, p.rows, p.cols, p.dres_in != nullptr) : 0;
+  if (odd > 0) {
+    const int64_t main_rows = p.rows - odd;
+    const int64_t mainP = bwd_pipeline_partial_rows(KIND, dt, main_rows, p.cols, p.dres_in != nullptr);
+    const size_t head = (size_t)mainP * NR * p.cols * sizeof(float);
+    if (mainP > 0 && (!want_params || (workspace != nullptr && is_aligned16(workspace) && workspace_bytes >= head))) {
+      BwdParams pm = p;
+      pm.rows = main_rows;
+      pm.partials = want_params ? reinterpret_cast<float*>(workspace) : nullptr;
+      pm.sync = nullptr;  // no column reduce in the kernel's tail
+      bool reduced = false;
+      int rc = launch_bwd_pipeline(KIND, dt, pm, st, &reduced);
+      if (rc != FLN_PIPE_NOT_APPLICABLE) {
+        if (rc != FLN_OK) return rc;
+        BwdParams pr = p;
+        const size_t off = (size_t)main_rows * (size_t)p.cols * sizeof(T);
+        pr.dy = static_cast<const unsigned char*>(p.dy) + off;
+        pr.x = static_cast<const unsigned char*>(p.x) + off;
+        if (p.dres_in != nullptr) pr.dres_in = static_cast<const unsigned char*>(p.dres_in) + off;
+        if (p.dx != nullptr) pr.dx = static_cast<unsigned char*>(p.dx) + off;
+        if (p.mean != nullptr) pr.mean = p.mean + main_rows;
+        pr.rstd = p.rstd + main_rows;
+        pr.rows = odd;
+        int64_t extra = 0;
+        rc = want_params ? run_bwd<T, KIND>(pr, nullptr, nullptr, nullptr, static_cast<unsigned char*>(workspace) + head,
+                                            workspace_bytes - head, aligned, st, &extra)
+                         : run_bwd<T, KIND>(pr, nullptr, nullptr, nullptr, nullptr, 0, aligned, st, nullptr);
+        if (rc != FLN_OK) return rc;
+        if (defer) {
+          *partial_rows_out = mainP + extra;
+          return FLN_OK;
+        }
+        if (want_params) {
+          launch_colreduce<T>(pm.partials, (int)(mainP + extra), NR * p.cols, p.cols, dgb_f32,
+                              reinterpret_cast<T*>(dgamma), reinterpret_cast<T*>(dbeta), st);
+          FLN_CHECK_LAUNCH();
+        }
+        return FLN_OK;
+      }
+    }
+  }
   const int64_t pipeP =
       aligned ? bwd_pipeline_partial_rows(KIND, dt, p.rows, p.cols, p.dres_in != nullptr) : 0;
   if (pipeP > 0) {
@@ -683,6 +727,22 @@ static size_t ws_bytes_typed(int64_t rows, int cols) {
   if (pipeP > P) P = pipeP;
   const int64_t pipeP3 = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows, cols, true);
   if (pipeP3 > P) P = pipeP3;
+  // a row count split between the pipeline and the register kernels (run_bwd): both sets of
+  // partial rows
+  for (int with_dres = 0; with_dres <= 1; ++with_dres) {
+    const int64_t odd = bwd_pipeline_odd_rows(dt, rows, cols, with_dres != 0);
+    if (odd > 0) {
+      const int64_t mainP = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, rows - odd, cols, with_dres != 0);
+      const BwdLaunch O = plan_bwd<T, FLN_LAYERNORM>(odd, cols, true);
+      const BwdLaunch O1 = plan_bwd<T, FLN_RMSNORM>(odd, cols, true);
+      int64_t oddP = O.P > O1.P ? O.P : O1.P;
+      // (the forced-pipeline test hook sends even these few rows through the pipeline)
+      const int64_t oddPipe = bwd_pipeline_partial_rows(FLN_LAYERNORM, dt, odd, cols, with_dres != 0);
+      if (oddPipe > oddP) oddP = oddPipe;
+      const int64_t both = mainP + oddP;
+      if (both > P) P = both;
+    }
+  }
   // + one 16-byte slot for the grid barrier of the fused column reduce
   return (((size_t)P * 2 * cols * sizeof(float) + 15) & ~(size_t)15) + 16;
 }

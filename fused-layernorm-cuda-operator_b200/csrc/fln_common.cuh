@@ -508,6 +508,12 @@ struct PipeDescription {
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out);
 // partial rows the pipelined backward writes for this shape (0 = not applicable)
 int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, bool with_dres);
+// Row counts that do not fill the row slots of the fast plan of their row length (2, 4, 8 or 16
+// rows per CTA) would run a bounds-checked or padded plan, 10 - 35 % slower.  These return how
+// many trailing rows to hand to the register kernels so that the rest runs the fast plan (0:
+// nothing to gain).
+int64_t fwd_pipeline_odd_rows(int act, int io_dtype, int out_dtype, const FwdParams& p);
+int64_t bwd_pipeline_odd_rows(int dtype, int64_t rows, int cols, bool with_dres);
 
 // ------------------------------------------------------------------------------------
 // host side: launch plan

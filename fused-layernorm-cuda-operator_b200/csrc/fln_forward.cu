@@ -402,8 +402,30 @@ extern "C" int fln_norm_forward(int kind, const void* x, const void* residual, c
   if (kind == FLN_RMSNORM && act != FLN_ACT_NONE) return FLN_ERR_UNSUPPORTED;
   if (aligned) {
     // large aligned problems: persistent bulk-async pipeline
-    const int rc = launch_fwd_pipeline(kind, act, io_dtype, out_dtype, p, st);
-    if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+    // (a row count that does not fill the fast plan's row slots: all but the last few rows
+    // through that plan, those through the register kernels below)
+    const int64_t odd = fwd_pipeline_odd_rows(act, io_dtype, out_dtype, p);
+    if (odd > 0) {
+      FwdParams pm = p;
+      pm.rows = p.rows - odd;
+      const int rc = launch_fwd_pipeline(kind, act, io_dtype, out_dtype, pm, st);
+      if (rc != FLN_PIPE_NOT_APPLICABLE) {
+        if (rc != FLN_OK) return rc;
+        const size_t es_in = io_dtype == FLN_F32 ? 4 : 2, es_out = out_dtype == FLN_F32 ? 4 : 2;
+        const size_t off = (size_t)pm.rows * (size_t)p.cols;
+        p.x = static_cast<const unsigned char*>(p.x) + off * es_in;
+        if (p.res != nullptr) p.res = static_cast<const unsigned char*>(p.res) + off * es_in;
+        if (p.sum_out != nullptr) p.sum_out = static_cast<unsigned char*>(p.sum_out) + off * es_in;
+        p.y = static_cast<unsigned char*>(p.y) + off * es_out;
+        if (p.mean != nullptr) p.mean += pm.rows;
+        if (p.rstd != nullptr) p.rstd += pm.rows;
+        p.rows = odd;
+      }
+    }
+    if (odd == 0 || p.rows != odd) {
+      const int rc = launch_fwd_pipeline(kind, act, io_dtype, out_dtype, p, st);
+      if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+    }
   }
   if (io_dtype == FLN_F32 && out_dtype == FLN_F32)
     return launch_kind_act<float, float>(kind, act, p, aligned, st);

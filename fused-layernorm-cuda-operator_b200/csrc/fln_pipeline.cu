@@ -370,6 +370,10 @@ PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres) {
 }
 
 bool describe_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, PipeDescription* out) {
+  // (a row count that does not fill the fast plan's row slots runs that plan on all but its last
+  // few rows)
+  rows -= backward ? bwd_pipeline_odd_rows(elem_bytes == 4 ? FLN_F32 : FLN_BF16, rows, cols, false)
+                   : fwd_plan_odd_rows(rows, cols, elem_bytes, 1, true);
   PipePlan P = backward ? plan_bwd_pipeline(rows, cols, elem_bytes, false) : plan_pipeline(false, rows, cols, elem_bytes, 1);
   if (!pipeline_wanted(P, rows)) return false;
   if (!backward && elem_bytes == 4 && cols <= 4096 && g_path_override.load(std::memory_order_relaxed) == 0) {
@@ -397,6 +401,31 @@ int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, b
   return P.pair ? (int64_t)(P.grid / 2) : (int64_t)P.grid * P.g.R;
 }
 
+
+int64_t fwd_plan_odd_rows(int64_t rows, int cols, int es, int tensors, bool allow_tail) {
+  if (rows < 32 || rows % 16 == 0) return 0;
+  // the plan a row count that fills every row slot would get: if this row count gets another
+  // one (a bounds-checked instantiation, or a later candidate with fewer rows per CTA), split
+  const int64_t main16 = rows - rows % 16;  // every plan's rows per CTA divide 16
+  const PipePlan M = plan_pipeline(false, main16, cols, es, tensors, true, allow_tail);
+  if (!M.ok || !(M.full || M.tail) || M.g.R <= 1 || !pipeline_wanted(M, main16)) return 0;
+  const PipePlan P = plan_pipeline(false, rows, cols, es, tensors, true, allow_tail);
+  if (P.ok && (P.full || P.tail) && P.K == M.K && P.vb == M.vb && P.g.tpr == M.g.tpr) return 0;
+  return rows % M.g.R;
+}
+
+int64_t bwd_pipeline_odd_rows(int dtype, int64_t rows, int cols, bool with_dres) {
+  const int es = dtype == FLN_F32 ? 4 : 2;
+  if (rows < 32 || rows % 16 == 0) return 0;
+  // the plan a row count that fills every row slot would get: if this row count gets another
+  // one (a bounds-checked instantiation, or a later candidate with fewer rows per CTA), split
+  const int64_t main16 = rows - rows % 16;  // every plan's rows per CTA divide 16
+  const PipePlan M = plan_bwd_pipeline(main16, cols, es, with_dres);
+  if (!M.ok || !(M.full || M.tail) || M.wide || M.pair || M.g.R <= 1 || !pipeline_wanted(M, main16)) return 0;
+  const PipePlan P = plan_bwd_pipeline(rows, cols, es, with_dres);
+  if (P.ok && (P.full || P.tail) && P.K == M.K && P.vb == M.vb && P.g.tpr == M.g.tpr) return 0;
+  return rows % M.g.R;
+}
 
 int path_override() { return g_path_override.load(std::memory_order_relaxed); }
 unsigned long long wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }

@@ -263,6 +263,8 @@ struct PipePlan {
 // tensors: how many input tensors are staged per tile (forward 1 or 2, backward 2 or 3)
 PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, int tensors,
                        bool allow_params_in_smem = true, bool allow_tail = true);
+// trailing rows to split off a forward so that the rest fills the row slots of the fast plan (0: none)
+int64_t fwd_plan_odd_rows(int64_t rows, int cols, int elem_bytes, int tensors, bool allow_tail);
 PipePlan plan_bwd_pipeline(int64_t rows, int cols, int es, bool with_dres);
 bool pipeline_wanted(const PipePlan& P, int64_t rows);
 int path_override();                  // fln_set_path_override

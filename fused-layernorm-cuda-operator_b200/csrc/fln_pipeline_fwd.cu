@@ -151,6 +151,11 @@ bool fwd_pipe_prepare(FwdParams* p) {
   return true;
 }
 
+int64_t fwd_pipeline_odd_rows(int act, int io_dtype, int out_dtype, const FwdParams& p0) {
+  const bool allow_tail = act == FLN_ACT_NONE && io_dtype == out_dtype;
+  return fwd_plan_odd_rows(p0.rows, p0.cols, io_dtype == FLN_F32 ? 4 : 2, p0.res != nullptr ? 2 : 1, allow_tail);
+}
+
 int launch_fwd_pipeline(int kind, int act, int io_dtype, int out_dtype, const FwdParams& p0,
                         cudaStream_t st) {
   const int es = io_dtype == FLN_F32 ? 4 : 2;

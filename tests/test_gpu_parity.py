@@ -778,9 +778,9 @@ def test_row_lengths_three_five_seven_times_a_power_of_two(path_override, shape,
                                    (2048, 1152), (1024, 2304), (512, 2880), (256, 7680), (128, 13824), (1024, 1000)])
 def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
     """Row lengths that fit no exact plan (1600 = 25 * 64, 4608 = 9 * 512): K vectors per thread of
-    which only the last is ragged.  The plan must be such a one where the rows fill the CTA's row
-    slots (4098 rows do not: the padded plan runs) and the row is within the backward's columns
-    per thread, results the checker's, forward with and without a residual, backward with and
+    which only the last is ragged.  The plan must be such a one (4098 rows do not fill the CTA's
+    row slots: the last two go through the register kernels) where the row is within the
+    backward's columns per thread, results the checker's, forward with and without a residual, backward with and
     without the incoming residual-stream gradient (the latter on the padded plan), two backward
     runs bit-identical."""
     path_override(2)
@@ -788,7 +788,7 @@ def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
     for backward in (False, True):
         d = capi.describe_launch(backward, rows, cols, dtype)
         # backward: up to 20 (16-bit) or 16 (fp32) columns for each of up to 512 threads
-        if rows != 4098 and (not backward or cols <= (8192 if dtype == F32 else 10240)):
+        if not backward or cols <= (8192 if dtype == F32 else 10240):
             k, t = d["vecs_per_thread"], d["threads_per_row"]
             nv = cols // (d["vector_bytes"] // dtype.itemsize)
             assert d["pipelined"] == 1 and 3 <= k <= 8
@@ -818,6 +818,62 @@ def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
             U.assert_param_grads_close(gb["dgb_f32"][cols:], wb["dbeta64"], wb["abs64"][1], rows)
         again = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
         assert torch.equal(gb["dx"], again["dx"]) and torch.equal(gb["dgb_f32"], again["dgb_f32"])
+    assert capi.lib().fln_device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("dtype", [BF16, F32, F16])
+@pytest.mark.parametrize("shape", [(4099, 4096), (4097, 1600), (4111, 768), (2051, 4608), (1025, 5120), (1035, 2048),
+                                   (33, 1024), (2049, 6144)])
+def test_row_counts_that_do_not_fill_the_row_slots(path_override, shape, dtype, kind):
+    """A row count that is no multiple of the fast plan's rows per CTA: all but the last few rows
+    run that plan, those few the register kernels, and the column sums cover both.  Forward with
+    and without a residual, backward with and without the incoming residual-stream gradient,
+    dx alone, the parameter gradients alone, and the two-step form that leaves the partial rows
+    to the caller."""
+    path_override(2)
+    rows, cols = shape
+    x, gamma, beta, dy, res = U.make_inputs(_seed(rows, cols) + 23, rows, cols, dtype, residual=True)
+    if kind == "rmsnorm":
+        beta = None
+    for r in (None, res):
+        got = U.run_forward(x, gamma, beta, r, kind)
+        want = O.norm_forward(x, gamma, beta, r, kind)
+        U.assert_out_close(got["y"], want["y"], dtype)
+        torch.testing.assert_close(got["rstd"], want["rstd"], rtol=1e-5, atol=1e-5)
+        if kind == "layernorm":
+            torch.testing.assert_close(got["mean"], want["mean"], rtol=1e-5, atol=1e-5)
+        if r is not None:
+            assert torch.equal(got["sum"].view(torch.uint8), want["sum"].view(torch.uint8))
+    f = O.norm_forward(x, gamma, beta, None, kind)
+    for dres in (None, res):
+        gb = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        wb = O.norm_backward(dy, x, f["mean"], f["rstd"], gamma, dres, kind)
+        if dtype == F32:
+            torch.testing.assert_close(gb["dx"], wb["dx32"], rtol=1e-5, atol=1e-5)
+        else:
+            U.assert_out_close(gb["dx"], wb["dx"], dtype)
+        U.assert_param_grads_close(gb["dgb_f32"][:cols], wb["dgamma64"], wb["abs64"][0], rows)
+        if kind == "layernorm":
+            U.assert_param_grads_close(gb["dgb_f32"][cols:], wb["dbeta64"], wb["abs64"][1], rows)
+        again = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, dres_in=dres)
+        assert torch.equal(gb["dx"], again["dx"]) and torch.equal(gb["dgb_f32"], again["dgb_f32"])
+    only_dx = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, want=(True, False, False), with_f32=False)
+    plain = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind)
+    assert torch.equal(only_dx["dx"], plain["dx"])
+    only_params = U.run_backward(dy, x, f["mean"], f["rstd"], gamma, kind, want=(False, True, True))
+    assert torch.equal(only_params["dgb_f32"], plain["dgb_f32"])
+    # the two-step form: partial rows now, their column sums by a second call
+    nr = 2 if kind == "layernorm" else 1
+    k = capi.LAYERNORM if kind == "layernorm" else capi.RMSNORM
+    ws = torch.empty(capi.backward_workspace_bytes(rows, cols, dtype) // 4, device="cuda")
+    dx2 = torch.empty(rows, cols, dtype=dtype, device="cuda")
+    md = f["mean"].cuda() if kind == "layernorm" else None
+    part = capi.norm_backward_partial(k, dy.cuda(), x.cuda(), md, f["rstd"].cuda(), gamma.cuda(), None, dx2, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(dx2.cpu(), plain["dx"]) and part.shape[1] == nr * cols
+    sums = part.double().sum(0).float().cpu()
+    torch.testing.assert_close(sums, plain["dgb_f32"], rtol=1e-4, atol=1e-3)
     assert capi.lib().fln_device_status() == 0
 
 
