@@ -581,7 +581,8 @@ def path_override():
 @pytest.mark.parametrize("mode", [1, 2, 3])  # 1 = register kernels, 2 = bulk-async pipeline, 3 = 2 with dgamma / dbeta summed by a second launch
 @pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
 @pytest.mark.parametrize("dtype", [F32, BF16, F16])
-@pytest.mark.parametrize("shape", [(701, 4096), (333, 8192), (1500, 768), (2049, 1024), (97, 16384), (4099, 256)])
+@pytest.mark.parametrize("shape", [(701, 4096), (333, 8192), (1500, 768), (2049, 1024), (97, 16384), (4099, 256),
+                                   (1008, 2048)])
 def test_kernel_families_agree_with_oracle(path_override, shape, dtype, kind, mode):
     path_override(mode)
     rows, cols = shape
@@ -612,11 +613,13 @@ def test_kernel_families_agree_with_oracle(path_override, shape, dtype, kind, mo
         torch.testing.assert_close(gr["dx"], wr["dx32"], rtol=1e-5, atol=1e-5)
     else:
         U.assert_out_close(gr["dx"], wr["dx"], dtype)
-    if cols <= (8192 if dtype == F32 else 12288):
+    if cols <= (8192 if dtype == F32 else 12288) and rows % 16 == 0:
         assert torch.equal(gr["dgb_f32"], gb["dgb_f32"])
     else:
         # longer rows: without the residual-stream gradient a row may be shared by the two CTAs
         # of a cluster, with it the long-row kernels run; the rows are then summed in another order
+        # (and so are row counts that do not fill the CTAs' row slots: the two forms may split the
+        # rows between the pipelined and the register kernels differently)
         U.assert_param_grads_close(gr["dgb_f32"][:cols], wr["dgamma64"], wr["abs64"][0], rows)
         if kind == "layernorm":
             U.assert_param_grads_close(gr["dgb_f32"][cols:], wr["dbeta64"], wr["abs64"][1], rows)
