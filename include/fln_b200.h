@@ -326,7 +326,9 @@ typedef struct {
   int64_t grid;      /* CTAs launched                                                     */
   int sm_count;
   int pipelined;     /* 1: the persistent bulk-async (TMA) pipeline serves this shape; the  */
-                     /* fields above then describe its plan                                */
+                     /* fields above then describe its plan (a row count that is no        */
+                     /* multiple of rows_per_cta: the plan of all but the last few rows,   */
+                     /* which the register kernels take)                                   */
   int stages;        /* shared-memory stages of that pipeline (0 otherwise)                */
   int vector_bytes;  /* bytes per vector access: 16, or 8 / 4 in the odd-K plans           */
 } fln_launch_info;
