@@ -173,7 +173,7 @@ PipePlan plan_pipeline(bool backward, int64_t rows, int cols, int elem_bytes, in
   const bool prefer_ragged = !backward && elem_bytes == 2 && K == 7 && vb == 8 &&
                              ((tensors == 1 && tpr == 512) || (wide_fwd && tpr >= 64));
   bool tail = false;
-  if (allow_tail && fK == 0 && tensors <= 2 &&
+  if (allow_tail && fK == 0 && tensors <= (backward ? 3 : 2) &&
       (K == 0 || (int64_t)K * tpr != cols / (vb / elem_bytes) || prefer_ragged)) {
     struct Cand {
       int k, vb;

@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(512) norm_bwd_pipe_kernel(const BwdParams p, c
   constexpr bool CT = LT >= 0;
   constexpr int LTC = CT ? LT : 0;
   static_assert(!CT || FULL, "compile-time geometry is for the FULL kernel");
-  static_assert(!TAIL || (CT && !DRES), "the ragged-last-vector kernel: split at compile time, plain stage 1");
+  static_assert(!TAIL || CT, "the ragged-last-vector kernel: split at compile time");
 // vector k of this thread lies in the row: known at compile time except for the last of a TAIL plan
 #define FLN_WHOLE(k) (FULL && !(TAIL && (k) == K - 1))
   static_assert(!PAIR || (LT == 9 && !FUSE && !DRES), "a shared row: 512 threads per half row, plain stage 1");

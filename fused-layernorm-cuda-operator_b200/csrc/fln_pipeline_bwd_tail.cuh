@@ -19,6 +19,16 @@ namespace fln {
 template <typename T, int KIND, int KK, int VB>
 static int bwd_tail_go(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
   const bool fuse = p.sync != nullptr;
+  // with an incoming gradient of the residual stream: the form with the column sums in the
+  // kernel's tail only (a caller that sums the partial rows itself runs the register kernels)
+  if (p.dres_in != nullptr) {
+    if (!fuse) return FLN_PIPE_NOT_APPLICABLE;
+#define FLN_TAIL_LT(L) \
+  if (P.g.tpr == (1 << L)) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, true, VB, L, false, true>, p, P, st);
+    FLN_TAIL_LT(6) FLN_TAIL_LT(7) FLN_TAIL_LT(8) FLN_TAIL_LT(9)
+#undef FLN_TAIL_LT
+    return FLN_PIPE_NOT_APPLICABLE;
+  }
 #define FLN_TAIL_LT(L)                                                                                                      \
   if (P.g.tpr == (1 << L)) {                                                                                                \
     if (fuse) return launch_bwd_kernel(norm_bwd_pipe_kernel<T, KK, KIND, true, true, false, VB, L, false, true>, p, P, st); \
@@ -57,7 +67,7 @@ static int bwd_tail_pair_go(const BwdParams& p, const PipePlan& P, cudaStream_t 
 
 template <typename T, int KIND>
 static int bwd_tail_kind(const BwdParams& p, const PipePlan& P, cudaStream_t st) {
-  if (!P.tail || P.threads != 512 || p.dres_in != nullptr) return FLN_PIPE_NOT_APPLICABLE;
+  if (!P.tail || P.threads != 512 || (p.dres_in != nullptr && (P.pair || P.bsm))) return FLN_PIPE_NOT_APPLICABLE;
 #define FLN_TAIL(KK, VBB)         \
   if (P.K == KK && P.vb == VBB) { \
     if (P.pair) return bwd_tail_pair_go<T, KIND, KK, VBB>(p, P, st); \
@@ -66,7 +76,7 @@ static int bwd_tail_kind(const BwdParams& p, const PipePlan& P, cudaStream_t st)
   if constexpr (sizeof(T) == 4) {
     FLN_TAIL(4, 16) FLN_TAIL(3, 16) FLN_TAIL(7, 8) FLN_TAIL(5, 8)
   } else {
-    if (P.K == 3 && P.vb == 16 && !P.pair) return bwd_tail_24_go<T, KIND>(p, P, st);
+    if (P.K == 3 && P.vb == 16 && !P.pair) return p.dres_in != nullptr ? FLN_PIPE_NOT_APPLICABLE : bwd_tail_24_go<T, KIND>(p, P, st);
     FLN_TAIL(5, 8) FLN_TAIL(4, 8) FLN_TAIL(3, 8) FLN_TAIL(7, 4)
   }
 #undef FLN_TAIL

@@ -784,8 +784,8 @@ def test_rows_with_a_ragged_last_vector(path_override, shape, dtype, kind):
     which only the last is ragged.  The plan must be such a one (4098 rows do not fill the CTA's
     row slots: the last two go through the register kernels) where the row is within the
     backward's columns per thread, results the checker's, forward with and without a residual, backward with and
-    without the incoming residual-stream gradient (the latter on the padded plan), two backward
-    runs bit-identical."""
+    without the incoming residual-stream gradient (which rides the same plans, long rows and the
+    24-column plan excepted), two backward runs bit-identical."""
     path_override(2)
     rows, cols = shape
     for backward in (False, True):
