@@ -477,7 +477,9 @@ using namespace fln;
 static int fp8_entry(int qmode, int kind, const void* x, const void* residual, const void* gamma,
                      const void* beta, void* q, void* sum_out, float* mean, float* rstd, float* amax,
                      float* scale, const float* scale_in, float* row_scale, int64_t rows, int64_t cols,
-                     int io_dtype, float eps, void* stream, unsigned char* block_scale = nullptr) {
+                     int io_dtype, float eps, void* stream, unsigned char* block_scale = nullptr,
+                     bool part = false) {
+  // part: a slice of the rows of a larger call (below) -- no further split, amax not reset
   if (kind != FLN_LAYERNORM && kind != FLN_RMSNORM) return FLN_ERR_ARG;
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return FLN_ERR_SHAPE;
   if (io_dtype != FLN_F32 && io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_ERR_DTYPE;
@@ -505,6 +507,30 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
   if (!(is_aligned16(x) && is_aligned16(residual) && is_aligned16(sum_out) && is_aligned16(q) &&
         is_aligned16(gamma) && is_aligned16(beta)))
     return FLN_ERR_UNSUPPORTED;
+
+  // A row count that does not fill the row slots of the pipelined plan (16-bit input, scale
+  // known before the launch): all but the last few rows through that plan, those through the
+  // register kernels; both fold their max |y| into the same word.
+  if (qmode != 0 && io_dtype != FLN_F32 && !part) {
+    const int64_t odd = fwd_fp8_pipeline_odd_rows(rows, (int)cols, residual != nullptr ? 2 : 1);
+    const int64_t m = rows - odd;
+    const size_t q_row = qmode == 4 ? (size_t)cols / 2 : (size_t)cols;
+    const size_t bs_row = qmode == 3 ? (size_t)cols / 32 : (qmode == 4 ? (size_t)cols / 16 : 0);
+    if (odd > 0 && ((size_t)m * q_row) % 16 == 0) {
+      if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+      int rc = fp8_entry(qmode, kind, x, residual, gamma, beta, q, sum_out, mean, rstd, amax, scale, scale_in,
+                         row_scale, m, cols, io_dtype, eps, stream, block_scale, true);
+      if (rc != FLN_OK) return rc;
+      const size_t off = (size_t)m * (size_t)cols * (size_t)es;
+      return fp8_entry(qmode, kind, static_cast<const unsigned char*>(x) + off,
+                       residual != nullptr ? static_cast<const unsigned char*>(residual) + off : nullptr, gamma, beta,
+                       static_cast<unsigned char*>(q) + (size_t)m * q_row,
+                       sum_out != nullptr ? static_cast<unsigned char*>(sum_out) + off : nullptr,
+                       mean != nullptr ? mean + m : nullptr, rstd != nullptr ? rstd + m : nullptr, amax, scale, scale_in,
+                       row_scale != nullptr ? row_scale + m : nullptr, odd, cols, io_dtype, eps, stream,
+                       block_scale != nullptr ? block_scale + (size_t)m * bs_row : nullptr, true);
+    }
+  }
 
   Fp8Params p;
   p.x = x;
@@ -560,7 +586,7 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
     f.drop_offset = 0;
     f.drop_threshold = 0;
     f.drop_scale = 1.f;
-    if (amax != nullptr && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
+    if (amax != nullptr && !part && cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return FLN_ERR_LAUNCH;
     const int rc = launch_fwd_pipeline_fp8(kind, io_dtype, qmode == 0 ? 1 : qmode, f, st);
     if (rc == FLN_OK) {
       if (qmode != 0) return FLN_OK;
@@ -569,6 +595,9 @@ static int fp8_entry(int qmode, int kind, const void* x, const void* residual, c
       return rc;
     }
   }
+  // (a slice: the register kernels must not reset amax either; for these forms the flag means
+  // nothing else)
+  if (part && qmode != 0) phase1_done = true;
 #define FLN_RUN(T)                                                                  \
   (kind == FLN_LAYERNORM ? run_fp8<T, FLN_LAYERNORM>(p, qmode, st, phase1_done)     \
                          : run_fp8<T, FLN_RMSNORM>(p, qmode, st, phase1_done))

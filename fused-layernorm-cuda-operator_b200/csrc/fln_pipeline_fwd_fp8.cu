@@ -33,13 +33,28 @@ static int fwd_pipe_fp8_typed(int kind, const FwdParams& p, const PipePlan& P, c
   return FLN_PIPE_NOT_APPLICABLE;
 }
 
+// the plans this file has instantiations for
+static bool fp8_plan_ok(const PipePlan& P, int64_t rows) {
+  return pipeline_wanted(P, rows) && P.full && P.vb == 16 && (P.K == 3 || P.K == 4) &&
+         P.threads == (P.g.tpr > 256 ? P.g.tpr : 256);
+}
+
+int64_t fwd_fp8_pipeline_odd_rows(int64_t rows, int cols, int tensors) {
+  if (rows < 32 || rows % 16 == 0) return 0;
+  const int64_t main16 = rows - rows % 16;  // every plan's rows per CTA divide 16
+  const PipePlan M = plan_pipeline(false, main16, cols, 2, tensors, false, false);
+  if (!fp8_plan_ok(M, main16) || M.g.R <= 1) return 0;
+  const PipePlan P = plan_pipeline(false, rows, cols, 2, tensors, false, false);
+  if (fp8_plan_ok(P, rows)) return 0;
+  return rows % M.g.R;
+}
+
 int launch_fwd_pipeline_fp8(int kind, int io_dtype, int qm, const FwdParams& p0, cudaStream_t st) {
   if (io_dtype != FLN_BF16 && io_dtype != FLN_F16) return FLN_PIPE_NOT_APPLICABLE;
   if (qm < 1 || qm > 4) return FLN_PIPE_NOT_APPLICABLE;
   // at most 32 elements per thread (gamma / beta in registers), no ragged last vector
   PipePlan P = plan_pipeline(false, p0.rows, p0.cols, 2, p0.res != nullptr ? 2 : 1, false, false);
-  if (!pipeline_wanted(P, p0.rows) || !P.full || P.vb != 16 || (P.K != 3 && P.K != 4)) return FLN_PIPE_NOT_APPLICABLE;
-  if (P.threads != (P.g.tpr > 256 ? P.g.tpr : 256)) return FLN_PIPE_NOT_APPLICABLE;
+  if (!fp8_plan_ok(P, p0.rows)) return FLN_PIPE_NOT_APPLICABLE;
   if ((qm == 3 && p0.cols % 32 != 0) || (qm == 4 && p0.cols % 16 != 0)) return FLN_PIPE_NOT_APPLICABLE;
   FwdParams p = p0;
   p.nv = p.cols / 8;

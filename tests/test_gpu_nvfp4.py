@@ -61,7 +61,7 @@ def test_nvfp4_block_scaled_output(shape, dtype, kind, residual):
         assert torch.equal(s.check().cpu().view(torch.uint8), want["sum"].view(torch.uint8))
 
 
-@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024)])
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024), (2051, 1024), (1031, 4096)])
 @pytest.mark.parametrize("dtype", [BF16, torch.float16])
 @pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
 def test_nvfp4_through_the_pipelined_forward(shape, dtype, kind, residual):

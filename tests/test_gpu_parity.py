@@ -319,11 +319,14 @@ def test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residu
 
 @pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("rmsnorm", False), ("layernorm", True)])
 @pytest.mark.parametrize("dtype", [BF16, F16])
-@pytest.mark.parametrize("shape", [(1024, 8192), (2048, 1024), (768, 3072), (512, 16384), (1200, 768)])
+@pytest.mark.parametrize("shape", [(1024, 8192), (2048, 1024), (768, 3072), (512, 16384), (1200, 768), (2051, 1024),
+                                   (1031, 4096), (1203, 768)])
 def test_fp8_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
     """Large 16-bit problems with a per-tensor scale are normalized by the persistent pipelined
     forward (forced here for medium sizes): the two-launch form (amax in the kernel) and the
-    delayed-scale form, 4 and 3 vectors per thread, against the checker; the statistics too."""
+    delayed-scale form, 4 and 3 vectors per thread, against the checker; the statistics too.
+    Row counts that do not fill the plan's row slots (2051, 1031, 1203): the one-pass forms hand
+    the last few rows to the register kernels, and amax covers both parts."""
     path_override(2)
     rows, cols = shape
     x, gamma, beta, _, res = U.make_inputs(20250 + cols, rows, cols, dtype, residual=residual, outliers=True)
@@ -404,7 +407,7 @@ def test_mxfp8_block_scaled_output(shape, dtype, kind, residual):
 
 @pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", True)])
 @pytest.mark.parametrize("dtype", [BF16, F16])
-@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024), (512, 16384)])
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024), (512, 16384), (2051, 1024), (1031, 4096)])
 def test_fp8_per_row_scales_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
     path_override(2)
     test_fp8_one_pass_with_delayed_and_per_row_scales(shape, dtype, kind, residual)
@@ -413,7 +416,7 @@ def test_fp8_per_row_scales_through_the_pipelined_forward(path_override, shape, 
 
 @pytest.mark.parametrize("kind,residual", [("rmsnorm", True), ("layernorm", False)])
 @pytest.mark.parametrize("dtype", [BF16, F16])
-@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024)])
+@pytest.mark.parametrize("shape", [(1024, 8192), (768, 3072), (2048, 1024), (2051, 1024), (1031, 4096)])
 def test_mxfp8_through_the_pipelined_forward(path_override, shape, dtype, kind, residual):
     """The same checks with the persistent pipelined forward doing the work (forced for these
     medium sizes; large 16-bit problems take it by themselves)."""
