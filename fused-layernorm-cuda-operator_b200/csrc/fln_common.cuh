@@ -514,7 +514,8 @@ int64_t bwd_pipeline_partial_rows(int kind, int dtype, int64_t rows, int cols, b
 // nothing to gain).
 int64_t fwd_pipeline_odd_rows(int act, int io_dtype, int out_dtype, const FwdParams& p);
 int64_t bwd_pipeline_odd_rows(int dtype, int64_t rows, int cols, bool with_dres);
-// (the quantizing forms of the pipelined forward: 16-bit input, `tensors` = 2 with a residual)
+// (the quantizing and dropout forms of the pipelined forward: 16-bit input, `tensors` = 2 with a
+// residual)
 int64_t fwd_fp8_pipeline_odd_rows(int64_t rows, int cols, int tensors);
 
 // ------------------------------------------------------------------------------------

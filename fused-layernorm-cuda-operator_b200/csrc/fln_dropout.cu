@@ -42,6 +42,7 @@ struct DropParams {
   float scale;
   unsigned int threshold;
   unsigned long long seed, offset;
+  int64_t row0;  // first row this launch takes (the rows before it went through the pipelined forward)
 };
 
 template <typename T>
@@ -111,7 +112,7 @@ __device__ __forceinline__ float cta_sum(float v, float* smem) {
 template <typename T, int K, int KIND>
 __global__ void __launch_bounds__(K == 4 ? 512 : 1024) dropout_add_norm_fwd_kernel(const DropParams p) {
   __shared__ float s_red[32];
-  const int64_t row = blockIdx.x;
+  const int64_t row = p.row0 + blockIdx.x;
   const int64_t base = row * (int64_t)p.cols;
   const T* __restrict__ x = reinterpret_cast<const T*>(p.x) + base;
   const T* __restrict__ res = p.res != nullptr ? reinterpret_cast<const T*>(p.res) + base : nullptr;
@@ -225,7 +226,7 @@ static int launch_drop_fwd(const DropParams& p, cudaStream_t st) {
   int threads = (p.groups + K - 1) / K;
   threads = (threads + 31) & ~31;
   if (threads > (K == 4 ? 512 : 1024)) return FLN_ERR_UNSUPPORTED;
-  const unsigned grid = (unsigned)p.rows;
+  const unsigned grid = (unsigned)(p.rows - p.row0);
   switch (K) {
     case 1:
       dropout_add_norm_fwd_kernel<T, 1, KIND><<<grid, threads, 0, st>>>(p);
@@ -279,6 +280,7 @@ extern "C" int fln_dropout_add_norm_forward(int kind, const void* x, const void*
   q.eps = eps;
   q.seed = seed;
   q.offset = offset;
+  q.row0 = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype != FLN_F32) {
     // large 16-bit problems: the persistent pipelined forward with the dropout folded in
@@ -311,8 +313,21 @@ extern "C" int fln_dropout_add_norm_forward(int kind, const void* x, const void*
     f.drop_offset = offset;
     f.drop_threshold = q.threshold;
     f.drop_scale = q.scale;
-    const int rc = launch_fwd_pipeline_dropout(kind, dtype, f, st);
-    if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+    // a row count that does not fill the pipelined plan's row slots: all but the last few rows
+    // through that plan, those through the kernel below (the mask depends on the element's
+    // position in the whole tensor, so both parts draw the bits an unsplit call would)
+    const int64_t odd = fwd_fp8_pipeline_odd_rows(rows, (int)cols, residual != nullptr ? 2 : 1);
+    if (odd > 0) {
+      f.rows = rows - odd;
+      const int rc = launch_fwd_pipeline_dropout(kind, dtype, f, st);
+      if (rc == FLN_OK) q.row0 = rows - odd;
+      else if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+      f.rows = rows;
+    }
+    if (q.row0 == 0) {
+      const int rc = launch_fwd_pipeline_dropout(kind, dtype, f, st);
+      if (rc != FLN_PIPE_NOT_APPLICABLE) return rc;
+    }
   }
 #define FLN_RUN(T) \
   (kind == FLN_LAYERNORM ? launch_drop_fwd<T, FLN_LAYERNORM>(q, st) : launch_drop_fwd<T, FLN_RMSNORM>(q, st))
